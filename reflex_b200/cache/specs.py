@@ -19,6 +19,9 @@ class KVSpec:
     # latent cache; the reference's attention parameters carry separate K and V
     # strides for it, src/kernels_cuda/attention_online.cu:22-23); None: head_dim
     v_head_dim: Optional[int] = None
+    # keys and values are the same rows (a latent that serves as both): the
+    # store then keeps one tensor and hands it out as keys and as values
+    shared_kv: bool = False
 
     @property
     def value_dim(self) -> int:

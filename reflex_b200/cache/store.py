@@ -60,7 +60,7 @@ class KVGroup:
         self.device = device
         if device is not None:
             self.k = torch.empty(shape, dtype=dtype, device=device)
-            self.v = torch.empty(v_shape, dtype=dtype, device=device)
+            self.v = self.k if spec.shared_kv else torch.empty(v_shape, dtype=dtype, device=device)
             self.table_dev = torch.zeros((max_slots, pages_per_seq), dtype=torch.int32, device=device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = self.table_dev = None

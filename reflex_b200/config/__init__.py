@@ -1,4 +1,5 @@
 from .spec import (  # noqa: F401
+    EmbeddingTermSpec,
     FeedForwardSpec,
     LayerSpec,
     MixerSpec,

@@ -2,9 +2,9 @@
 
 The reference dispatches on the checkpoint's architecture string
 (src/model/mod.rs:800-826; accepted names src/model/config.rs:231-239).  Here
-the string comes from config.json: `architectures[0]` (e.g. "Qwen3ForCausalLM")
-or `model_type` (e.g. "qwen3"); both keys of an architecture point at the same
-entry.  An entry has two functions: `parse(config dict) -> typed config` and
+the string comes from config.json: `architectures[0]` (e.g. "Qwen3ForCausalLM"),
+`model_type` (e.g. "qwen3") or `architecture` (e.g. "Kegasun"); all keys of an
+architecture point at the same entry.  An entry has two functions: `parse(config dict) -> typed config` and
 `build(typed config) -> ModelSpec`.  Adding an architecture is one
 `register_architecture` call from a new module under `reflex_b200/models/`.
 """
@@ -53,6 +53,8 @@ def resolve_architecture(cfg: Dict[str, Any]) -> Architecture:
         candidates.extend(str(a) for a in archs)
     if cfg.get("model_type") is not None:
         candidates.append(str(cfg["model_type"]))
+    if isinstance(cfg.get("architecture"), str):  # some config files name it in the singular
+        candidates.append(cfg["architecture"])
     for c in candidates:
         if c in _ARCHITECTURES:
             return _ARCHITECTURES[c]

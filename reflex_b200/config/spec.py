@@ -24,7 +24,7 @@ from typing import Any, Dict, List, Optional, Tuple
 class NormSpec:
     """A normalisation over the last dimension of `size` elements."""
 
-    kind: str  # "rmsnorm"
+    kind: str  # "rmsnorm"; "layernorm" (mean taken off, a weight and no bias)
     size: int
     eps: float
     # y = x * r * (weight_offset + w); 0.0 is the reference's plain weight
@@ -60,16 +60,46 @@ class MixerSpec:
     qk_norm: Optional[NormSpec] = None
     position: Optional[PositionSpec] = None
     names: Tuple[Tuple[str, str], ...] = ()
+    # what only some kinds have, by name: "latent_attention" reads q_rank, kv_rank,
+    # eps and sink; "mlstm" reads gate_cap and eps
     params: Tuple[Tuple[str, Any], ...] = ()
+    # size of a head's value vector when it differs from `head_dim`; 0: the same
+    v_head_dim: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+    def param(self, name: str, default: Any = None) -> Any:
+        return dict(self.params).get(name, default)
 
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str  # "swiglu"
+    kind: str  # "swiglu"; "moe" (params: experts, top, activation, router_bias)
     hidden_size: int
     intermediate_size: int
     names: Tuple[Tuple[str, str], ...] = ()
     params: Tuple[Tuple[str, Any], ...] = ()
+
+    def param(self, name: str, default: Any = None) -> Any:
+        return dict(self.params).get(name, default)
+
+
+@dataclass(frozen=True)
+class EmbeddingTermSpec:
+    """Something added to the token embedding before the first layer: a
+    registered embedding term (`reflex_b200.parts.embedding`), e.g.
+    "bigram_hash" (params: buckets, mul_prev, mul_cur) or "sinusoidal" (params:
+    base)."""
+
+    kind: str
+    hidden_size: int
+    names: Tuple[Tuple[str, str], ...] = ()
+    params: Tuple[Tuple[str, Any], ...] = ()
+
+    def param(self, name: str, default: Any = None) -> Any:
+        return dict(self.params).get(name, default)
 
 
 @dataclass(frozen=True)
@@ -81,9 +111,9 @@ class LayerSpec:
     block: str  # "prenorm"
     prefix: str
     mixer: MixerSpec
-    feed_forward: FeedForwardSpec
+    feed_forward: Optional[FeedForwardSpec]  # None: the layer is its mixer alone
     mixer_norm: NormSpec
-    feed_forward_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
     names: Tuple[Tuple[str, str], ...] = ()
     # further norms of the arrangement, by role (sandwich norms after the mixer and
     # after the feed-forward, before the residual add: src/model/dense.rs:72-83,
@@ -127,6 +157,8 @@ class ModelSpec:
     logit_scale: float = 1.0
     bos_token_id: Optional[int] = None
     eos_token_ids: Tuple[int, ...] = ()
+    # terms added to the token embedding, in order
+    embedding_terms: Tuple[EmbeddingTermSpec, ...] = ()
 
     def __post_init__(self) -> None:
         if not self.run_order:

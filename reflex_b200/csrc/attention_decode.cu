@@ -71,6 +71,7 @@ __device__ __forceinline__ void dtrace_value(int launch, int which, long long v)
 }
 
 constexpr int PAGE = 64;
+constexpr float LOG2E = 1.4426950408889634f;
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_STAGES = 3;  // pages in flight per CTA
 constexpr int MAX_RANKS = 16;  // 8 is the portable cluster size; 16 where the device places one
@@ -84,8 +85,9 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const __nv_bfloat16* __restrict__ v_pages, PagedKV cache,
                         const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
-                        int n_htiles, int n_splits, int window, float scale_log2, int cluster_merge,
-                        int trace_id, int* __restrict__ err) {
+                        int n_htiles, int n_splits, int window, float scale_log2,
+                        const float* __restrict__ sink, int cluster_merge, int trace_id,
+                        int* __restrict__ err) {
     constexpr int LD = D + 8;
     constexpr int TILE = TMA ? PAGE * D : PAGE * LD;  // elements of a page's key (or value) tile
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -391,6 +393,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         const size_t head = (size_t)r * nq + h0 + row;
         if (n_splits == 1) {
+            // a sink adds exp(sink - max) to the denominator, once, with no value
+            if (sink) L += exp2f(sink[h0 + row] * LOG2E - M);
             out[head * D + e] = __float2bfloat16_rn(A / L);
         } else if (!cluster_merge) {
             float* p = partial + (head * n_splits + split) * (D + 2);
@@ -433,6 +437,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 L = __fadd_rn(L, __fmul_rn(recv_l[sidx * 16 + row], f));
                 A += recv_a[(size_t)sidx * slice + off] * f;
             }
+            if (sink) L = __fadd_rn(L, exp2f(sink[h0 + row] * LOG2E - M));
             const float inv = 1.0f / L;
             out[((size_t)r * nq + h0 + row) * D + e] = __float2bfloat16_rn(A * inv);
         }
@@ -444,7 +449,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 // The splits' weights 2^(m_s - M) / L are computed once into shared memory.
 constexpr int MAX_SPLITS = 64;
 __global__ void attention_combine_kernel(const float* __restrict__ partial,
-                                         __nv_bfloat16* __restrict__ out, int D, int n_splits) {
+                                         __nv_bfloat16* __restrict__ out, int D, int n_splits,
+                                         const float* __restrict__ sink, int nq) {
     __shared__ float wgt[MAX_SPLITS];
     __shared__ float lw[MAX_SPLITS];
     __shared__ float inv_l;
@@ -480,6 +486,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial,
             if (threadIdx.x == 0) {  // in split order, by one lane: the same bits every time
                 float L = 0.0f;
                 for (int sidx = 0; sidx < n_splits; ++sidx) L += lw[sidx];
+                if (sink && !dry) L = __fadd_rn(L, exp2f(sink[head % nq] * LOG2E - M));
                 inv_l = 1.0f / L;
             }
         }
@@ -517,8 +524,8 @@ const CUtensorMap* store_map(const void* base, long long rows, int D) {
 template <int D, bool TMA>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, long long pool_pages,
                   const PagedKV& cache, const int* row_pos, const int* row_slot, void* out, float* partial,
-                  int R, int nq, int n_splits, int window, float scale, int cluster_merge, int* err,
-                  cudaStream_t s) {
+                  int R, int nq, int n_splits, int window, float scale, const float* sink, int cluster_merge,
+                  int* err, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     const int n_htiles = (g + 7) / 8;
@@ -570,18 +577,19 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
                     cluster_merge ? n_splits : 1, *mk, *mv,
                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                     cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-                    scale * 1.4426950408889634f, cluster_merge, g_dtrace_next++, err);
+                    scale * LOG2E, sink, cluster_merge, g_dtrace_next++, err);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1 && !cluster_merge)
         RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
-                   (__nv_bfloat16*)out, D, n_splits);
+                   (__nv_bfloat16*)out, D, n_splits, sink, nq);
     return 0;
 }
 
 int decode_entry(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                  int max_pages, int page_size, const int* row_pos, const int* row_slot, void* out,
                  float* partial, int R, int nq, int nkv, int head_dim, int n_splits, int window,
-                 float scale, int cluster_merge, long long pool_pages, int* err, void* stream) {
+                 float scale, const float* sink, int cluster_merge, long long pool_pages, int* err,
+                 void* stream) {
     if (R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
     if (n_splits > 1 && !partial && !cluster_merge) return RFX_ERR_BAD_ARG;
@@ -601,7 +609,7 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
                      pool_pages * nkv * PAGE < 2147483647LL;
 #define RFX_GO(DD, T)                                                                                     \
     launch_decode<DD, T>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, R, nq, \
-                         n_splits, window, scale, cluster_merge, err, s)
+                         n_splits, window, scale, sink, cluster_merge, err, s)
 #define RFX_CASE(DD)                                        \
     case DD:                                                \
         if (DD % 64 == 0 && tma) {                          \
@@ -633,10 +641,11 @@ extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const vo
                                     const int* page_table, int max_pages, int page_size,
                                     const int* row_pos, const int* row_slot, void* out,
                                     float* partial, int R, int nq, int nkv, int head_dim,
-                                    int n_splits, int window, float scale, long long pool_pages,
-                                    int* err, void* stream) {
+                                    int n_splits, int window, float scale, const float* sink,
+                                    long long pool_pages, int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        partial, R, nq, nkv, head_dim, n_splits, window, scale, 0, pool_pages, err, stream);
+                        partial, R, nq, nkv, head_dim, n_splits, window, scale, sink, 0, pool_pages, err,
+                        stream);
 }
 
 // The same with 2, 4, 8 or (where the device places such a cluster) 16 splits that
@@ -650,9 +659,11 @@ extern "C" int rfx_attention_decode_cluster(const void* q, const void* k_pages, 
                                             const int* page_table, int max_pages, int page_size,
                                             const int* row_pos, const int* row_slot, void* out, int R,
                                             int nq, int nkv, int head_dim, int n_splits, int window,
-                                            float scale, long long pool_pages, int* err, void* stream) {
+                                            float scale, const float* sink, long long pool_pages,
+                                            int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, 1, pool_pages, err, stream);
+                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, sink, 1, pool_pages, err,
+                        stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -722,5 +733,5 @@ extern "C" int rfx_attention_decode_noalloc(const void* q, const void* k_pages, 
     // before the combine reads it, so nothing in the array has to start at zero
     return rfx_attention_decode(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos,
                                 row_slot, out, scratch, R, nq, nkv, head_dim, n_splits, window, scale,
-                                0, nullptr, stream);
+                                nullptr, 0, nullptr, stream);
 }

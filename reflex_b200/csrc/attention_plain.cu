@@ -31,7 +31,8 @@ __global__ void __launch_bounds__(128)
 attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                        const T* __restrict__ v_pages, PagedKV cache,
                        const int* __restrict__ row_pos, const int* __restrict__ row_slot,
-                       T* __restrict__ out, int nq, int window, float scale) {
+                       T* __restrict__ out, int nq, int window, float scale,
+                       const float* __restrict__ sink) {
     pdl_prologue();
     const int d = cache.head_dim;
     const int r = blockIdx.x;
@@ -73,6 +74,16 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         }
         m = m_new;
     }
+    if (sink) {
+        // the sink is one more term of the denominator: exp(sink - max), with no
+        // key and no value; the maximum takes it in like a score
+        const float sv = sink[h];
+        const float m_new = fmaxf(m, sv);
+        const float corr = exact_expf(m - m_new);
+        l = fmaf(l, corr, exact_expf(sv - m_new));
+#pragma unroll
+        for (int i = 0; i < MAX_PER_LANE; ++i) acc[i] *= corr;
+    }
     T* orow = out + ((size_t)r * nq + h) * d;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -87,7 +98,7 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
                                    const int* page_table, int max_pages, int page_size,
                                    const int* row_pos, const int* row_slot, void* out, int R,
                                    int nq, int nkv, int head_dim, int window, float scale,
-                                   void* stream) {
+                                   const float* sink, void* stream) {
     if (R <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
     if (nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
@@ -98,11 +109,11 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(attention_plain_kernel<float>, grid, 128, 0, s, (const float*)q,
                    (const float*)k_pages, (const float*)v_pages, cache, row_pos, row_slot,
-                   (float*)out, nq, window, scale);
+                   (float*)out, nq, window, scale, sink);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(attention_plain_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)q,
                    (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos,
-                   row_slot, (__nv_bfloat16*)out, nq, window, scale);
+                   row_slot, (__nv_bfloat16*)out, nq, window, scale, sink);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

@@ -30,7 +30,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
                          __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
-                         float scale_log2) {
+                         float scale_log2, const float* __restrict__ sink) {
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [128][LD]
@@ -127,7 +127,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         const int row = warp_row0 + (lane >> 2) + 8 * h;
         if (row >= n_rows) continue;
         const int p = row / g, hd = row % g;
-        const float inv = 1.0f / l[h];
+        // a sink adds exp(sink - max) to the denominator, once, with no value
+        const float inv = 1.0f / (sink ? l[h] + exp2f(sink[kvh * g + hd] * 1.4426950408889634f - m[h]) : l[h]);
         __nv_bfloat16* o = out + ((size_t)(row0 + q0 + p) * nq + kvh * g + hd) * D + 2 * (lane & 3);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
@@ -141,7 +142,7 @@ template <int D>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const PagedKV& cache,
                    const int* seq_slot, const int* seq_start, const int* seq_new,
                    const int* seq_row0, void* out, int S, int max_new, int nq, int window,
-                   float scale, cudaStream_t s) {
+                   float scale, const float* sink, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     if (g > PF_ROWS) return RFX_ERR_UNSUPPORTED;
@@ -154,7 +155,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, PF_THREADS, smem, s, (const __nv_bfloat16*)q,
                (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, seq_slot, seq_start,
-               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f);
+               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink);
     return 0;
 }
 
@@ -168,7 +169,8 @@ extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const v
                                      const int* page_table, int max_pages, int page_size,
                                      const int* seq_slot, const int* seq_start, const int* seq_new,
                                      const int* seq_row0, void* out, int S, int max_new, int nq,
-                                     int nkv, int head_dim, int window, float scale, void* stream) {
+                                     int nkv, int head_dim, int window, float scale, const float* sink,
+                                     void* stream) {
     if (S <= 0 || max_new <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
@@ -176,7 +178,7 @@ extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const v
 #define RFX_CASE(DD)                                                                              \
     case DD:                                                                                      \
         return launch_prefill<DD>(q, k_pages, v_pages, cache, seq_slot, seq_start, seq_new,       \
-                                  seq_row0, out, S, max_new, nq, window, scale, s);
+                                  seq_row0, out, S, max_new, nq, window, scale, sink, s);
     switch (head_dim) {
         RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
         RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)

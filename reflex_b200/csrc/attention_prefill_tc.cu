@@ -113,7 +113,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
                             __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
-                            float scale_log2, int* __restrict__ err) {
+                            float scale_log2, const float* __restrict__ sink, int* __restrict__ err) {
     static_assert(D == 64 || D == 128, "head sizes 64 and 128");
     constexpr int KB = D / 64;                 // 64-column blocks of a row
     constexpr int KV_BYTES = PAGE * D * 2;
@@ -383,7 +383,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         if (ok && n_pages > 0) {
             tc_fence_after_sync();
-            const float inv = 1.0f / l;
+            // a sink adds exp(sink - reference) to the denominator, once, with no value
+            const float inv = 1.0f / (sink ? l + ex2(fmaf(sink[kvh * g + row_h], 1.4426950408889634f, -m)) : l);
             __nv_bfloat16* o = out + ((size_t)(row0 + q0 + row_p) * nq + kvh * g + row_h) * D;
             // two loads of 16 columns in flight: the next one travels while this one is stored
             uint32_t rr[2][16];
@@ -437,7 +438,7 @@ template <int D>
 int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long n_pages_total,
               const PagedKV& cache, const int* seq_slot, const int* seq_start, const int* seq_new,
               const int* seq_row0, void* out, int S, int max_new, int R, int nq, int window, float scale,
-              int* err, cudaStream_t s) {
+              const float* sink, int* err, cudaStream_t s) {
     const int g = nq / cache.n_kv_heads;
     if (g > ROWS) return RFX_ERR_UNSUPPORTED;
     const int bq = ROWS / g;
@@ -454,7 +455,7 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
     dim3 grid(cache.n_kv_heads, S, (max_new + bq - 1) / bq);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, THREADS, smem, s, mq, mk, mv, cache, seq_slot, seq_start, seq_new, seq_row0,
-               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, err);
+               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, err);
     return 0;
 }
 
@@ -477,7 +478,7 @@ extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, cons
                                         int page_size, const int* seq_slot, const int* seq_start,
                                         const int* seq_new, const int* seq_row0, void* out, int S,
                                         int max_new, int R, int nq, int nkv, int head_dim, int window,
-                                        float scale, int* err, void* stream) {
+                                        float scale, const float* sink, int* err, void* stream) {
     if (S <= 0 || max_new <= 0 || R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) |
@@ -487,9 +488,9 @@ extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, cons
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch_tc<64>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
-                             seq_row0, out, S, max_new, R, nq, window, scale, err, s);
+                             seq_row0, out, S, max_new, R, nq, window, scale, sink, err, s);
     if (head_dim == 128)
         return launch_tc<128>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
-                              seq_row0, out, S, max_new, R, nq, window, scale, err, s);
+                              seq_row0, out, S, max_new, R, nq, window, scale, sink, err, s);
     return RFX_ERR_UNSUPPORTED;
 }

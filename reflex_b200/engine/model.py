@@ -16,7 +16,8 @@ import torch
 from .. import ops
 from ..cache.specs import KVSpec, StateSpec
 from ..config.spec import ModelSpec, RunEntry
-from ..parts.registry import BLOCKS, NORMS, TensorInfo
+from ..config.spec import names_dict
+from ..parts.registry import BLOCKS, EMBEDDING_TERMS, NORMS, TensorInfo
 
 
 @dataclass
@@ -34,6 +35,10 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[str, ...], Tensor
     """tensor name -> (where it goes, TensorInfo) for the whole model."""
     out: Dict[str, Tuple[Tuple[str, ...], TensorInfo]] = {}
     out[spec.embedding_name] = (("embedding",), TensorInfo((spec.vocab_size, spec.hidden_size), "table"))
+    for ti, term in enumerate(spec.embedding_terms):
+        names = names_dict(term.names)
+        for role, info in EMBEDDING_TERMS.get(term.kind).tensor_specs(term).items():
+            out[names.get(role, role)] = (("embedding_term", str(ti), role), info)
     for li, layer in enumerate(spec.layers):
         for name, (part, role, info) in BLOCKS.get(layer.block).tensor_names(layer).items():
             out[name] = (("layer", str(li), part, role), info)
@@ -52,6 +57,7 @@ class CausalLM:
         self.device = torch.device(device)
         self.layers = [BLOCKS.get(l.block)(l, dtype, self.device) for l in spec.layers]
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm, dtype, self.device)
+        self.embedding_terms = [EMBEDDING_TERMS.get(t.kind)(t, dtype, self.device) for t in spec.embedding_terms]
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
 
@@ -65,6 +71,7 @@ class CausalLM:
         attribute out or sets it False, and the engine then runs every step
         eagerly."""
         return (all(bool(getattr(l, "capturable", False)) for l in self.layers)
+                and all(bool(getattr(t, "capturable", False)) for t in self.embedding_terms)
                 and bool(getattr(self.final_norm, "capturable", False)))
 
     # --- weights ----------------------------------------------------------
@@ -72,6 +79,7 @@ class CausalLM:
         """`tensors`: every name of `expected_tensors`, already checked."""
         exp = expected_tensors(self.spec)
         per_layer: Dict[int, Dict[str, Dict[str, torch.Tensor]]] = {}
+        per_term: Dict[int, Dict[str, torch.Tensor]] = {}
         for name, (where, _info) in exp.items():
             t = tensors[name]
             if where[0] == "embedding":
@@ -80,11 +88,15 @@ class CausalLM:
                 self.head = t.to(device=self.device, dtype=self.dtype).contiguous()
             elif where[0] == "final_norm":
                 self.final_norm.bind({"weight": t})
+            elif where[0] == "embedding_term":
+                per_term.setdefault(int(where[1]), {})[where[2]] = t
             else:
                 _, li, part, role = where
                 per_layer.setdefault(int(li), {}).setdefault(part, {})[role] = t
         for li, layer in enumerate(self.layers):
             layer.bind(per_layer.get(li, {}))
+        for ti, term in enumerate(self.embedding_terms):
+            term.bind(per_term.get(ti, {}))
         if self.spec.tie_word_embeddings:
             self.head = self.embedding  # the same storage, no copy
 
@@ -94,7 +106,17 @@ class CausalLM:
         for entry, li in self.spec.cache_entries().items():
             mixer = self.layers[li].mixer
             out[entry] = mixer.cache_spec() if hasattr(mixer, "cache_spec") else None
+        # what the embedding's terms keep per sequence: entries below zero, beside the runs' own
+        for ti, term in enumerate(self.embedding_terms):
+            st = term.state_spec()
+            if st is not None:
+                out[self.term_entry(ti)] = st
         return out
+
+    @staticmethod
+    def term_entry(index: int) -> int:
+        """Cache entry of embedding term `index` (the runs' entries count from zero up)."""
+        return -1 - index
 
     # --- forward ----------------------------------------------------------
     def hidden_states(self, batch, cache) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -103,6 +125,9 @@ class CausalLM:
         # gives a zero row and sets the device's error word, which `check_errors` reads
         h = ops.embed(self.embedding, batch.tokens, self.spec.embedding_scale,
                       ops.device_error_word(self.device))
+        for ti, term in enumerate(self.embedding_terms):
+            entry = self.term_entry(ti)
+            term.add(h, batch, cache.state(entry) if cache.has(entry) == "state" else None)
         ops.prof_mark("embed")
         pending = None
         order = self.spec.run_order

@@ -467,14 +467,18 @@ FUSE_QKV_ROWS = _env_int("REFLEX_B200_FUSE_QKV_ROWS", 8, 0, 64)
 def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     page_table: torch.Tensor, page_size: int, row_pos: torch.Tensor,
                     row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
-                    window: Optional[int], scale: float) -> torch.Tensor:
+                    window: Optional[int], scale: float,
+                    sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`sink` (float32, one per query head): exp(sink) joins the softmax's
+    denominator once, with no key and no value."""
     R = q.shape[0]
     out = _new(q.shape, q.dtype, q.device)
     st = native.lib().rfx_attention_plain(
         _chk(q, "q"), _chk(k_pages, "k_pages", q.dtype), _chk(v_pages, "v_pages", q.dtype),
         dt_code(q.dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1],
         page_size, _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
-        out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale), _stream())
+        out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale),
+        _chk(sink, "sink", torch.float32), _stream())
     native.check(st, f"attention_plain (head_dim={head_dim})")
     return out
 
@@ -543,7 +547,8 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
 
 
 def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv,
-                     head_dim, window, scale, n_splits: Optional[int] = None) -> torch.Tensor:
+                     head_dim, window, scale, n_splits: Optional[int] = None,
+                     sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 tensor-core attention for rows that are each one query
     position (decode), split over the keys."""
     R = q.shape[0]
@@ -561,8 +566,8 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
             q.data_ptr(), _chk(k_pages, "k_pages", torch.bfloat16), _chk(v_pages, "v_pages", torch.bfloat16),
             _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
             _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
-            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), pool_pages,
-            device_error_word(q.device).data_ptr(), _stream())
+            R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), _chk(sink, "sink", torch.float32),
+            pool_pages, device_error_word(q.device).data_ptr(), _stream())
         if st != native.ERR_UNSUPPORTED:
             native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
             return out
@@ -572,7 +577,8 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
         partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
-        int(window or 0), float(scale), pool_pages, device_error_word(q.device).data_ptr(), _stream())
+        int(window or 0), float(scale), _chk(sink, "sink", torch.float32), pool_pages,
+        device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
     return out
 
@@ -581,7 +587,7 @@ CLUSTER_MERGE = _env_flag("REFLEX_B200_CLUSTER_MERGE", True)
 
 
 def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
-                      seq_row0, max_new: int, nq, nkv, head_dim, window, scale) -> torch.Tensor:
+                      seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None) -> torch.Tensor:
     """bfloat16 tensor-core attention for a packed batch of sequences that
     each bring one or more rows (prefill, chunks, mixed steps)."""
     _chk(q, "q", torch.bfloat16)
@@ -596,13 +602,14 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
-        S, int(max_new), nq, nkv, head_dim, int(window or 0), float(scale), _stream())
+        S, int(max_new), nq, nkv, head_dim, int(window or 0), float(scale),
+        _chk(sink, "sink", torch.float32), _stream())
     native.check(st, f"attention_prefill (head_dim={head_dim})")
     return out
 
 
 def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
-                         seq_row0, max_new: int, nq, nkv, head_dim, window, scale) -> torch.Tensor:
+                         seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None) -> torch.Tensor:
     """The tcgen05/TMEM form of `attention_prefill`, for head sizes 64 and 128."""
     _chk(q, "q", torch.bfloat16)
     if head_dim not in (64, 128):
@@ -616,30 +623,219 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
         seq_slot.numel(), int(max_new), q.shape[0], nq, nkv, head_dim, int(window or 0), float(scale),
-        device_error_word(q.device).data_ptr(), _stream())
+        _chk(sink, "sink", torch.float32), device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_prefill_tc (head_dim={head_dim})")
     return out
 
 
-def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale):
+def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale,
+              sink=None):
     """Attention of the step's rows over their sequences' cached keys and
-    values; picks the kernel for the dtype and the kind of step."""
+    values; picks the kernel for the dtype and the kind of step.  `sink`: one
+    float32 per query head whose exponential joins the softmax's denominator."""
     fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if fast and batch.is_decode:
         pages = -(-min(batch.max_context, window or batch.max_context) // page_size) + (1 if window else 0)
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale,
-                                n_splits=decode_splits(q.shape[0], nq, nkv, pages))
+                                n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink)
     if fast and nq // nkv <= 128 and head_dim in (64, 128):
         return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                     batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                    nkv, head_dim, window, scale)
+                                    nkv, head_dim, window, scale, sink)
     if fast and nq // nkv <= 128:
         return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                  batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                 nkv, head_dim, window, scale)
+                                 nkv, head_dim, window, scale, sink)
     return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
-                           batch.row_slot, nq, nkv, head_dim, window, scale)
+                           batch.row_slot, nq, nkv, head_dim, window, scale, sink)
+
+
+# ------------------------------------------------- further norms and embedding terms
+def layernorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+              delta: Optional[torch.Tensor] = None, update_residual: bool = True,
+              rows: Optional[torch.Tensor] = None, want_out: bool = True) -> Optional[torch.Tensor]:
+    """Layer norm with a weight and no bias of the float32 residual stream `x`
+    [R, H], the residual add fused in as in `rmsnorm`: t = x (+ delta);
+    returns (t - mean) / sqrt(var + eps) * weight in `out_dtype`."""
+    R, H = x.shape
+    _chk(x, "x", torch.float32)
+    r_out = R if rows is None else rows.numel()
+    out = _new((r_out, H), out_dtype, x.device) if want_out else None
+    x_out = x if (delta is not None and update_residual and rows is None) else None
+    st = native.lib().rfx_layernorm(
+        x.data_ptr(), _chk(delta, "delta"), dt_code(delta.dtype) if delta is not None else 0,
+        x_out.data_ptr() if x_out is not None else 0, _chk(weight, "weight", torch.float32),
+        float(eps), out.data_ptr() if out is not None else 0, dt_code(out_dtype),
+        _chk(rows, "rows", torch.int32), r_out, H, _stream())
+    native.check(st, f"layernorm (H={H})")
+    return out
+
+
+def bigram_add(hidden: torch.Tensor, table: torch.Tensor, batch, prev_state: torch.Tensor,
+               mul_prev: int, mul_cur: int, vocab: int) -> torch.Tensor:
+    """hidden[r] += table[(prev * mul_prev + token * mul_cur) mod buckets], the
+    table's last row at a sequence's first position; `prev_state` (int32, one
+    word a slot) holds each sequence's last token between steps."""
+    R, H = hidden.shape
+    buckets = table.shape[0] - 1
+    st = native.lib().rfx_bigram_add(
+        _chk(hidden, "hidden", torch.float32), _chk(table, "table"), dt_code(table.dtype),
+        _chk(batch.tokens, "tokens", torch.int32), _chk(batch.row_pos, "row_pos", torch.int32),
+        _chk(batch.row_slot, "row_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
+        batch.seq_slot.numel(), _chk(prev_state, "prev_state", torch.int32), R, H, buckets,
+        int(mul_prev), int(mul_cur), int(vocab), _stream())
+    native.check(st, "bigram_add")
+    return hidden
+
+
+def sinusoid_add(hidden: torch.Tensor, row_pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """hidden[r, 2i] += sin(p f_i), hidden[r, 2i + 1] += cos(p f_i); `inv_freq`
+    float64 [ceil(H / 2)]."""
+    R, H = hidden.shape
+    if inv_freq.numel() != (H + 1) // 2:
+        raise InvalidInput("sinusoid_add: one frequency per pair of columns is needed")
+    st = native.lib().rfx_sinusoid_add(_chk(hidden, "hidden", torch.float32),
+                                       _chk(row_pos, "row_pos", torch.int32),
+                                       _chk(inv_freq, "inv_freq", torch.float64), R, H, _stream())
+    native.check(st, "sinusoid_add")
+    return hidden
+
+
+# ---------------------------------------------------------- latent attention
+def latent_post(proj: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float,
+                row_pos, row_slot, pages, page_table, page_size: int, q_rank: int, kv_rank: int,
+                n_gate: int, writes_cache: bool, out_dtype: torch.dtype):
+    """A row of the stacked product [query latent | key/value latent | gates]:
+    RMSNorm of the query latent (returned, `out_dtype`), RMSNorm of the
+    key/value latent into the cache at the row's position, sigmoid of the gates
+    (returned, float32 [R, n_gate])."""
+    R = proj.shape[0]
+    q = _new((R, q_rank), out_dtype, proj.device)
+    gate = _new((R, max(1, n_gate)), torch.float32, proj.device)
+    st = native.lib().rfx_latent_post(
+        _chk(proj, "proj"), dt_code(proj.dtype), proj.shape[1], _chk(q_weight, "q_weight", torch.float32),
+        _chk(kv_weight, "kv_weight", torch.float32), float(eps), _chk(row_pos, "row_pos", torch.int32),
+        _chk(row_slot, "row_slot", torch.int32), q.data_ptr(), _chk(pages, "pages", out_dtype),
+        dt_code(out_dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
+        gate.data_ptr(), R, q_rank, kv_rank, n_gate, 1 if writes_cache else 0, _stream())
+    native.check(st, "latent_post")
+    return q, gate
+
+
+HEADS_LINEAR_MAX_ROWS = _env_int("REFLEX_B200_HEADS_LINEAR_MAX_ROWS", 64, 0, 1 << 30)
+
+
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[r, b, :] = x[r, b, :] @ weight[b].T for every head b: x [R, heads * K],
+    weight [heads, N, K], y [R, heads * N]; with `scale` (float32 [R, heads])
+    y[r, b, :] is multiplied by scale[r, b].  float32 and a few bfloat16 rows:
+    this library's kernel (32-bit accumulation in index order); more bfloat16
+    rows: the library's batched product, then the scaling kernel."""
+    heads, N, K = weight.shape
+    R = x.shape[0]
+    if x.shape[1] != heads * K or x.dtype != weight.dtype:
+        raise InvalidInput("heads_linear: x must be [rows, heads * K] in the weight's dtype")
+    _chk(x, "x")
+    _chk(weight, "weight")
+    y = _new((R, heads * N), x.dtype, x.device)
+    if x.dtype == torch.bfloat16 and R > HEADS_LINEAR_MAX_ROWS:
+        torch.bmm(x.view(R, heads, K).transpose(0, 1), weight.transpose(1, 2),
+                  out=y.view(R, heads, N).transpose(0, 1))
+        if scale is not None:
+            st = native.lib().rfx_scale_heads(y.data_ptr(), dt_code(y.dtype), _chk(scale, "scale", torch.float32),
+                                              y.numel(), N, _stream())
+            native.check(st, "scale_heads")
+        return y
+    st = native.lib().rfx_heads_linear(x.data_ptr(), heads * K, weight.data_ptr(), y.data_ptr(), heads * N,
+                                       dt_code(x.dtype), _chk(scale, "scale", torch.float32), R, N, K, heads,
+                                       _stream())
+    native.check(st, f"heads_linear (heads={heads}, N={N}, K={K})")
+    return y
+
+
+# --------------------------------------------------------------------- mLSTM
+MLSTM_SLICE = 64  # columns of the memory a block of the scan owns; each slice keeps its own copy of m
+
+
+def mlstm_state_floats(dim: int, vdim: int) -> int:
+    """Floats of state per head and slot: S [dim, vdim], n [dim], m once per slice."""
+    return dim * vdim + dim + (vdim + MLSTM_SLICE - 1) // MLSTM_SLICE
+
+
+def mlstm_scan(proj: torch.Tensor, offsets, bias_i, bias_f, cap: float, q_scale: float, batch,
+               state: torch.Tensor, heads: int, dim: int, vdim: int):
+    """The recurrence over the step's rows, sequence by sequence.  `proj`
+    float32 [R, ld] holds q, k, v and the two gate pre-activations at the
+    column offsets `offsets` = (q, k, v, i, f); `state` [slots, heads, floats].
+    Returns the numerators S^T q [R, heads * vdim] and denominators [R, heads]."""
+    R = proj.shape[0]
+    _chk(proj, "proj", torch.float32)
+    if state.shape[-1] != mlstm_state_floats(dim, vdim) or state.shape[-2] != heads:
+        raise InvalidInput("mlstm_scan: the state's shape does not match the sizes")
+    num = _new((R, heads * vdim), torch.float32, proj.device)
+    den = _new((R, heads), torch.float32, proj.device)
+    q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
+    st = native.lib().rfx_mlstm_scan(
+        proj.data_ptr(), proj.shape[1], q_off, k_off, v_off, i_off, f_off,
+        _chk(bias_i, "bias_i", torch.float32), _chk(bias_f, "bias_f", torch.float32), float(cap),
+        float(q_scale), _chk(batch.seq_slot, "seq_slot", torch.int32),
+        _chk(batch.seq_row0, "seq_row0", torch.int32), batch.seq_slot.numel(),
+        _chk(state, "state", torch.float32), num.data_ptr(), den.data_ptr(), heads, dim, vdim, _stream())
+    native.check(st, f"mlstm_scan (dim={dim}, vdim={vdim})")
+    return num, den
+
+
+def mlstm_out(num, den, proj, g_off: int, weight, eps: float, heads: int, vdim: int,
+              out_dtype: torch.dtype) -> torch.Tensor:
+    """o = num / den, each head's o over its root mean square, times the norm
+    weight [heads * vdim], times sigmoid of the gate columns of `proj`."""
+    R = num.shape[0]
+    out = _new((R, heads * vdim), out_dtype, num.device)
+    st = native.lib().rfx_mlstm_out(num.data_ptr(), den.data_ptr(), _chk(proj, "proj", torch.float32),
+                                    proj.shape[1], int(g_off), _chk(weight, "weight", torch.float32),
+                                    float(eps), out.data_ptr(), dt_code(out_dtype), R, heads, vdim, _stream())
+    native.check(st, "mlstm_out")
+    return out
+
+
+# ------------------------------------------------------- mixture of experts
+MOE_ACTIVATIONS = {"relu2": 0, "silu": 1}
+
+
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """Router logits float32 [R, experts] (+ bias) -> ids int32 [R, top], the
+    experts with the largest logits, and weights float32 [R, top], the softmax
+    over the chosen logits only."""
+    R, E = logits.shape
+    ids = _new((R, top), torch.int32, logits.device)
+    wts = _new((R, top), torch.float32, logits.device)
+    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32), _chk(bias, "bias", torch.float32),
+                                    ids.data_ptr(), wts.data_ptr(), R, E, int(top), _stream())
+    native.check(st, f"moe_route (experts={E}, top={top})")
+    return ids, wts
+
+
+def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+                wts: torch.Tensor, activation: str = "relu2") -> torch.Tensor:
+    """sum_k wts[r, k] down[e] act(up[e] x[r]), e = ids[r, k]; up [experts, ff,
+    width], down [experts, width, ff]; float32 [R, width].  Every (row, choice)
+    reads its expert's matrices itself: the form for a few rows, and the exact
+    one in 32-bit."""
+    R, width = x.shape
+    E, ff, _w = up.shape
+    top = ids.shape[1]
+    act = _new((R * top, ff), x.dtype, x.device)
+    st = native.lib().rfx_moe_up(_chk(x, "x"), _chk(up, "up", x.dtype), _chk(ids, "ids", torch.int32),
+                                 act.data_ptr(), dt_code(x.dtype), R, top, ff, width,
+                                 MOE_ACTIVATIONS[activation], _stream())
+    native.check(st, "moe_up")
+    y = _new((R, width), torch.float32, x.device)
+    st = native.lib().rfx_moe_down(act.data_ptr(), _chk(down, "down", x.dtype), ids.data_ptr(),
+                                   _chk(wts, "wts", torch.float32), y.data_ptr(), dt_code(x.dtype), R, top,
+                                   ff, width, _stream())
+    native.check(st, "moe_down")
+    return y
 
 
 # ------------------------------------------------------------------ sampling

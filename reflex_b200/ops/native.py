@@ -40,19 +40,39 @@ _SIGNATURES = {
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong,
-                             c_void_p, c_void_p],
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                             c_longlong, c_void_p, c_void_p],
     "rfx_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_longlong,
-                                     c_void_p, c_void_p],
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                     c_longlong, c_void_p, c_void_p],
     "rfx_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_void_p],
+                              c_float, c_void_p, c_void_p],
     "rfx_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_int, c_float, c_void_p, c_void_p],
+                                 c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
+    "rfx_layernorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
+                      c_int, c_int, c_void_p],
+    "rfx_bigram_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                       c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p],
+    "rfx_sinusoid_add": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "rfx_latent_post": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                        c_void_p],
+    "rfx_heads_linear": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                         c_int, c_void_p],
+    "rfx_scale_heads": [c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
+    "rfx_mlstm_scan": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                       c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                       c_void_p],
+    "rfx_mlstm_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
+                      c_int, c_int, c_void_p],
+    "rfx_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_down": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p],
     "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -83,6 +103,8 @@ def lib() -> ctypes.CDLL:
             fn.restype = c_int
         handle.rfx_gemm_bf16_tc_max_parts.argtypes = [c_int]
         handle.rfx_gemm_bf16_tc_max_parts.restype = c_int
+        handle.rfx_mlstm_state_floats.argtypes = [c_int, c_int]
+        handle.rfx_mlstm_state_floats.restype = c_int
         handle.rfx_sm_count.argtypes = []
         handle.rfx_sm_count.restype = c_int
         handle.rfx_sample_work_bytes.argtypes = [c_int, c_int]

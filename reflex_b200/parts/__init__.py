@@ -1,5 +1,6 @@
 from .registry import (  # noqa: F401
     BLOCKS,
+    EMBEDDING_TERMS,
     FEED_FORWARDS,
     MIXERS,
     NORMS,
@@ -7,9 +8,10 @@ from .registry import (  # noqa: F401
     Rotation,
     TensorInfo,
     register_block,
+    register_embedding_term,
     register_feed_forward,
     register_mixer,
     register_norm,
     register_position,
 )
-from . import norm, rope, mlp, attention, block  # noqa: F401,E402  (registers the parts)
+from . import norm, rope, mlp, attention, block, embedding, latent_attention, mlstm, moe  # noqa: F401,E402  (registers the parts)

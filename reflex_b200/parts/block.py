@@ -22,10 +22,14 @@ class PreNormBlock:
     def __init__(self, spec: LayerSpec, dtype: torch.dtype, device):
         self.spec = spec
         self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, dtype, device)
-        self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
-            spec.feed_forward_norm, dtype, device)
         self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device)
-        self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+        # a layer may be its mixer alone
+        self.has_feed_forward = spec.feed_forward is not None
+        self.feed_forward_norm = self.feed_forward = None
+        if self.has_feed_forward:
+            self.feed_forward_norm = NORMS.get(spec.feed_forward_norm.kind)(
+                spec.feed_forward_norm, dtype, device)
+            self.feed_forward = FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
 
     @property
     def fusable_first_norm(self):
@@ -37,8 +41,10 @@ class PreNormBlock:
     @property
     def capturable(self) -> bool:
         """Whether every part of the layer allows its launches to be captured."""
-        return all(bool(getattr(p, "capturable", False))
-                   for p in (self.mixer_norm, self.feed_forward_norm, self.mixer, self.feed_forward))
+        parts = [self.mixer_norm, self.mixer]
+        if self.has_feed_forward:
+            parts += [self.feed_forward_norm, self.feed_forward]
+        return all(bool(getattr(p, "capturable", False)) for p in parts)
 
     @classmethod
     def tensor_names(cls, spec: LayerSpec) -> Dict[str, Tuple[str, str, TensorInfo]]:
@@ -48,24 +54,31 @@ class PreNormBlock:
 
         def add(part: str, infos: Dict[str, TensorInfo], names: Dict[str, str]) -> None:
             for role, info in infos.items():
-                suffix = names.get(role, role)
+                # "role#7": one of several tensors of a kind (an expert's); the
+                # name pattern of the kind is filled with the index
+                base, _, index = role.partition("#")
+                suffix = names.get(base, base)
+                if index:
+                    suffix = suffix.format(expert=index)
                 out[spec.prefix + suffix] = (part, role, info)
 
         add("mixer_norm", {"weight": NORMS.get(spec.mixer_norm.kind).tensor_specs(spec.mixer_norm)["weight"]},
             {"weight": block_names.get("mixer_norm", "mixer_norm.weight")})
-        add("feed_forward_norm",
-            {"weight": NORMS.get(spec.feed_forward_norm.kind).tensor_specs(spec.feed_forward_norm)["weight"]},
-            {"weight": block_names.get("feed_forward_norm", "feed_forward_norm.weight")})
         add("mixer", MIXERS.get(spec.mixer.kind).tensor_specs(spec.mixer), names_dict(spec.mixer.names))
-        add("feed_forward", FEED_FORWARDS.get(spec.feed_forward.kind).tensor_specs(spec.feed_forward),
-            names_dict(spec.feed_forward.names))
+        if spec.feed_forward is not None:
+            add("feed_forward_norm",
+                {"weight": NORMS.get(spec.feed_forward_norm.kind).tensor_specs(spec.feed_forward_norm)["weight"]},
+                {"weight": block_names.get("feed_forward_norm", "feed_forward_norm.weight")})
+            add("feed_forward", FEED_FORWARDS.get(spec.feed_forward.kind).tensor_specs(spec.feed_forward),
+                names_dict(spec.feed_forward.names))
         return out
 
     def bind(self, by_part: Dict[str, Dict[str, torch.Tensor]]) -> None:
         self.mixer_norm.bind(by_part.get("mixer_norm", {}))
-        self.feed_forward_norm.bind(by_part.get("feed_forward_norm", {}))
         self.mixer.bind(by_part.get("mixer", {}))
-        self.feed_forward.bind(by_part.get("feed_forward", {}))
+        if self.has_feed_forward:
+            self.feed_forward_norm.bind(by_part.get("feed_forward_norm", {}))
+            self.feed_forward.bind(by_part.get("feed_forward", {}))
 
     def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
         """`pending` is what the block before left: a delta still to be added to
@@ -80,6 +93,11 @@ class PreNormBlock:
         else:
             x = self.mixer_norm(hidden, delta=pending)
             ops.prof_mark("norm")
+        if not self.has_feed_forward:
+            # the mixer's result is the layer's: the next norm takes it up
+            if getattr(self.mixer, "supports_fused_residual", False):
+                return hidden, self.mixer.forward(x, ctx, residual=(hidden, next_norm))
+            return hidden, self.mixer.forward(x, ctx)
         if getattr(self.mixer, "supports_fused_residual", False):
             ffn_norm = self.feed_forward_norm if getattr(self.feed_forward, "accepts_normed_input", False) else None
             a = self.mixer.forward(x, ctx, residual=(hidden, ffn_norm))

@@ -39,3 +39,30 @@ class RMSNorm:
         return ops.rmsnorm(residual, self.weight, self.spec.eps, self.dtype, delta=delta,
                            update_residual=update, rows=rows,
                            weight_offset=self.spec.weight_offset)
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    """y = (x - mean) / sqrt(var + eps) * w over the last dimension, var the
+    mean of the squared deviations; a weight and no bias; statistics in 32-bit.
+    The residual add that precedes it is fused in, as with `RMSNorm`."""
+
+    capturable = True
+
+    def __init__(self, spec: NormSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def tensor_specs(cls, spec: NormSpec) -> Dict[str, TensorInfo]:
+        return {"weight": TensorInfo((spec.size,), "norm")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def __call__(self, residual: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                 rows: Optional[torch.Tensor] = None, update: bool = True) -> torch.Tensor:
+        return ops.layernorm(residual, self.weight, self.spec.eps, self.dtype, delta=delta,
+                             update_residual=update, rows=rows)

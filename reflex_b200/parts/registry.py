@@ -23,6 +23,8 @@ Interfaces (duck-typed; `spec` is the part's record from `config.spec`):
                   forward(x, ctx) -> delta [rows, hidden]
   feed-forward    forward(x) -> delta [rows, hidden]
   block           forward(hidden_f32, pending_delta, ctx) -> (hidden_f32, pending_delta)
+  embedding term  state_spec() -> StateSpec | None
+                  add(hidden_f32, batch, state)       adds itself to the rows in place
 """
 
 from __future__ import annotations
@@ -39,6 +41,7 @@ class TensorInfo:
     # "matrix": a linear layer's weight, kept in the compute dtype, drawn N(0, 0.02)
     # "table":  an embedding table, same
     # "norm":   a norm's weight, kept 32-bit, drawn 1 + U(-0.1, 0.1)
+    # "bias":   a bias or another small vector, kept 32-bit, drawn U(-0.5, 0.5)
     role: str
     optional: bool = False
 
@@ -94,9 +97,11 @@ FEED_FORWARDS = _Registry("feed-forward")
 NORMS = _Registry("norm")
 POSITIONS = _Registry("position encoding")
 BLOCKS = _Registry("block arrangement")
+EMBEDDING_TERMS = _Registry("embedding term")
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position = POSITIONS.register
 register_block = BLOCKS.register
+register_embedding_term = EMBEDDING_TERMS.register
