@@ -38,13 +38,13 @@ __global__ void bigram_add_kernel(float* __restrict__ hidden, const T* __restric
             }
             prev_state[slot] = tokens[seq_row0[lo + 1] - 1];
         }
-        int row = buckets;
+        int row = buckets;  // a sequence's first position: the extra row, whatever the state holds
         if (row_pos[r] != 0) {
             long long v = ((long long)prev * mul_prev + (long long)tok * mul_cur) % (long long)buckets;
             if (v < 0) v += buckets;
-            row = (int)v;
+            row = (prev < 0 || prev >= vocab) ? -1 : (int)v;
         }
-        if (tok < 0 || tok >= vocab || prev < 0 || prev >= vocab) row = -1;  // the embedding reports it
+        if (tok < 0 || tok >= vocab) row = -1;  // an id outside the vocabulary: the embedding reports it
         s_row = row;
     }
     __syncthreads();
