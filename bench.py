@@ -247,6 +247,162 @@ class Arm:
         return {"tok_s": n / s, "seconds": s, "tokens": n, "steps": new_tokens}
 
 
+# ---- a second design beside the closest existing one, at equal sizes (--design) ----
+# Layer sizes that resemble a real model's; `kv_rank` stays within what the
+# tensor-core attention kernels take (256).  The Qwen3 model beside each has the
+# same width, depth, head count, head size, feed-forward width, vocabulary and
+# attention span (all layers slide over the same window).
+DESIGN_SIZES = {
+    "w1024": {"width": 1024, "layers": 8, "heads": 8, "dim": 128, "q_rank": 384, "kv_rank": 128, "window": 1024,
+              "m_heads": 4, "m_dim": 128, "m_vdim": 256, "ff": 4096, "experts": 8, "top": 2, "expert_ff": 2048,
+              "vocab": 32768},
+    "w2048": {"width": 2048, "layers": 8, "heads": 16, "dim": 128, "q_rank": 768, "kv_rank": 256, "window": 1024,
+              "m_heads": 8, "m_dim": 128, "m_vdim": 256, "ff": 8192, "experts": 16, "top": 4, "expert_ff": 2048,
+              "vocab": 32768},
+    "w4096": {"width": 4096, "layers": 4, "heads": 32, "dim": 128, "q_rank": 1536, "kv_rank": 256, "window": 1024,
+              "m_heads": 16, "m_dim": 128, "m_vdim": 256, "ff": 12288, "experts": 16, "top": 4, "expert_ff": 3072,
+              "vocab": 32768},
+}
+
+
+def kegasun_config(z):
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": z["heads"], "dim": z["dim"], "vdim": z["dim"], "q_rank": z["q_rank"],
+                     "kv_rank": z["kv_rank"], "mask": {"size": z["window"]}, "scale": z["dim"] ** -0.5}}
+    rec = {"type": "mlstm", "mixer": {"heads": z["m_heads"], "dim": z["m_dim"], "vdim": z["m_vdim"], "gate_cap": 15.0}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    pattern = [(rec, dense), (lat, moe), (lat, dense), (lat, moe)]
+    layers = [dict(pattern[i % 4][0], mlp=pattern[i % 4][1]) for i in range(z["layers"])]
+    return {"architecture": "Kegasun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 127, "mul_cur": 7}},
+            "layers": layers}
+
+
+def qwen3_config_like(z):
+    cfg = dict(QWEN3_8B)
+    cfg.update({"num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
+                "num_key_value_heads": max(1, z["heads"] // 4), "head_dim": z["dim"], "intermediate_size": z["ff"],
+                "vocab_size": z["vocab"], "use_sliding_window": True, "sliding_window": z["window"],
+                "layer_types": ["sliding_attention"] * z["layers"]})
+    return cfg
+
+
+def design_comparison(args) -> int:
+    """Prefill and decode throughput of the Kegasun design beside Qwen3 at equal
+    sizes, with every phase's time in a prefill and in a decode step."""
+    import torch
+
+    from reflex_b200 import ops
+    from reflex_b200.api import Model
+    from reflex_b200.weights import random_model_on_device
+
+    pk = peaks()
+    torch.cuda.set_device(0)
+    T, B, P, steps = PREFILL_TOKENS, args.batch, PROMPT, max(16, min(args.steps, 64))
+    out = {"metric": "prefill and decode tokens/s, Kegasun beside Qwen3 at equal sizes", "unit": "tokens/s",
+           "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
+           "prefill_tokens": T, "decode_batch": B, "decode_prompt": P, "decode_steps": steps,
+           "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "of": pk["source"]}, "sizes": {}}
+    names = [n for n in args.sizes.split(",") if n]
+    for name in names:
+        z = DESIGN_SIZES[name]
+        row = {}
+        for design, cfg in (("kegasun", kegasun_config(z)), ("qwen3", qwen3_config_like(z))):
+            lm = random_model_on_device(cfg, 0, torch.bfloat16, "cuda:0")
+            model = Model(lm, max_tokens=B * (P + steps + 128) + T + 256, max_batch=B)
+            eng = model.engine
+            g = torch.Generator().manual_seed(1)
+            V = z["vocab"]
+            prompt = torch.randint(0, V, (T,), generator=g).tolist()
+            times = []
+            for i in range(4):
+                s = eng.open()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                a.record()
+                logits = eng.step([(s, prompt, [T - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                eng.close(s)
+                if i:
+                    times.append(a.elapsed_time(b))
+            finite = bool(torch.isfinite(logits).all().item())
+            pms = min(times)
+            # decode: B sequences from P-token prompts, ids fed from the device
+            prompts = torch.randint(0, V, (B, P), generator=g).tolist()
+            seqs = [eng.open() for _ in range(B)]
+            logits = eng.step([(s, p, [P - 1]) for s, p in zip(seqs, prompts)])
+            ids = [torch.empty((B,), dtype=torch.int32, device="cuda:0") for _ in range(2)]
+            scratch = torch.empty((B * 128,), dtype=torch.float32, device="cuda:0")
+            ops.argmax(logits, out=ids[0], scratch=scratch)
+            for i in range(4):
+                logits = eng.step_decode(seqs, ids[i % 2], borrow=True)
+                ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for i in range(4, 4 + steps):
+                logits = eng.step_decode(seqs, ids[i % 2], borrow=True)
+                ops.argmax(logits, out=ids[(i + 1) % 2], scratch=scratch)
+            b.record()
+            torch.cuda.synchronize()
+            dms = a.elapsed_time(b) / steps
+            finite = finite and bool(torch.isfinite(logits).all().item())
+            launches = eng.launches_per_decode_step(B)
+            # every phase's time: one eager prefill and one eager decode step with events at the marks
+            ops.PROFILE = True
+            eng.use_graphs = False
+            s = eng.open()
+            eng.step([(s, prompt, [T - 1])])
+            phases_prefill = {k: round(v, 4) for k, v in ops.LAST_PROFILE.items()}
+            eng.close(s)
+            eng.step([(q, [1], [0]) for q in seqs])
+            eng.step([(q, [1], [0]) for q in seqs])
+            phases_decode = {k: round(v, 4) for k, v in ops.LAST_PROFILE.items()}
+            ops.PROFILE = False
+            for q in seqs:
+                eng.close(q)
+            eng.check_errors()
+            weight_bytes = sum(t.numel() * t.element_size() for t in _model_tensors(lm))
+            row[design] = {"prefill_ms": pms, "prefill_tok_s": T * 1000.0 / pms, "decode_ms": dms,
+                           "decode_tok_s": B * 1000.0 / dms, "decode_launches": launches, "finite": finite,
+                           "weight_bytes": weight_bytes, "phases_prefill_ms": phases_prefill,
+                           "phases_decode_ms": phases_decode}
+            del model, eng, lm
+            import gc
+
+            gc.collect()
+            torch.cuda.empty_cache()
+        row["prefill_ratio"] = row["kegasun"]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
+        row["decode_ratio"] = row["kegasun"]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
+        out["sizes"][name] = row
+    print(json.dumps(out))
+    return 0
+
+
+def _model_tensors(lm):
+    """Every weight tensor a model's parts hold (for a count of bytes)."""
+    import torch
+
+    seen, out = set(), []
+
+    def walk(o, depth=0):
+        if isinstance(o, torch.Tensor):
+            if o.is_cuda and o.data_ptr() not in seen:
+                seen.add(o.data_ptr())
+                out.append(o)
+        elif isinstance(o, (list, tuple)):
+            for x in o:
+                walk(x, depth + 1)
+        elif hasattr(o, "__dict__") and depth < 4:
+            for x in vars(o).values():
+                walk(x, depth + 1)
+
+    walk(lm)
+    return out
+
+
 def main() -> int:
     global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
@@ -263,7 +419,13 @@ def main() -> int:
                     help="workloads beside the headline: 14b and 32b add their points (default: all)")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the decode steps")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cache positions per sequence")
+    ap.add_argument("--design", default="", choices=["", "kegasun"],
+                    help="instead of the headline: this design beside Qwen3 at equal sizes (prefill, decode, phases)")
+    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="with --design: which of the sizes " +
+                    ", ".join(sorted(DESIGN_SIZES)))
     args = ap.parse_args()
+    if args.design and args.impl == "ours":
+        return design_comparison(args)
     PROMPT = args.prompt
     CONTEXT = max(args.context, args.prompt + max(args.steps, 0 if args.no_points else POINT_STEPS) + args.warmup + 64)
 

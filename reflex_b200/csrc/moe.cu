@@ -9,6 +9,11 @@
 //  * rfx_moe_down: y[r, :] = sum_k wts[r, k] W_down[ids[r, k]] act[(r, k), :],
 //    the experts in the order of their rank, 32-bit sums: a row's result does
 //    not depend on the batch.
+//  * Many rows (prefill): rfx_moe_group places the (row, choice) pairs expert by
+//    expert (counts, offsets, each pair's place), rfx_moe_gather copies the
+//    rows into that order, the library multiplies each expert's block by its
+//    matrices, rfx_moe_activation applies f in place, and rfx_moe_combine sums
+//    a row's `top` results in the order of their rank with their weights.
 // Expert weights are stacked: W_up [experts, ff, width], W_down [experts, width, ff].
 #include "common.cuh"
 
@@ -66,6 +71,47 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
         for (int k = 32; k < top; ++k) wts[(size_t)r * top + k] /= sum;
 }
 
+// sum_c xs[c] * w[c] over a warp; bfloat16 rows that start on 16 bytes go eight
+// elements a load.  The order depends on n and the row's alignment alone.
+template <typename T>
+__device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const T* __restrict__ w, int n,
+                                          int lane) {
+    float dot = 0.0f;
+    int c0 = 0;
+    if constexpr (sizeof(T) == 2) {
+        if ((n & 7) == 0 && ((reinterpret_cast<uintptr_t>(w) | (uintptr_t)__cvta_generic_to_shared(xs)) & 15) == 0) {
+            const uint4* w8 = reinterpret_cast<const uint4*>(w);
+            const int n8 = n / 8;
+            for (int v0 = lane; v0 < n8; v0 += 128) {  // four loads in flight a lane
+                uint4 u[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    u[j] = v0 + 32 * j < n8 ? w8[v0 + 32 * j] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (v0 + 32 * j >= n8) break;
+                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u[j]);
+                    const float4* xv = reinterpret_cast<const float4*>(xs + 8 * (v0 + 32 * j));
+                    const float4 x0 = xv[0], x1 = xv[1];
+                    const float2 f0 = __bfloat1622float2(p[0]), f1 = __bfloat1622float2(p[1]);
+                    const float2 f2 = __bfloat1622float2(p[2]), f3 = __bfloat1622float2(p[3]);
+                    dot = fmaf(x0.x, f0.x, dot);
+                    dot = fmaf(x0.y, f0.y, dot);
+                    dot = fmaf(x0.z, f1.x, dot);
+                    dot = fmaf(x0.w, f1.y, dot);
+                    dot = fmaf(x1.x, f2.x, dot);
+                    dot = fmaf(x1.y, f2.y, dot);
+                    dot = fmaf(x1.z, f3.x, dot);
+                    dot = fmaf(x1.w, f3.y, dot);
+                }
+            }
+            c0 = n / 8 * 8;
+        }
+    }
+    for (int c = c0 + lane; c < n; c += 32) dot = fmaf(xs[c], ld<T>(w, c), dot);
+    return warp_sum(dot);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ x, const T* __restrict__ W, const int* __restrict__ ids,
@@ -81,9 +127,7 @@ moe_up_kernel(const T* __restrict__ x, const T* __restrict__ W, const int* __res
     const T* We = W + (size_t)e * ff * width;
     for (int j = blockIdx.y * nwarps + warp; j < ff; j += gridDim.y * nwarps) {
         const T* wrow = We + (size_t)j * width;
-        float dot = 0.0f;
-        for (int c = lane; c < width; c += 32) dot = fmaf(xs[c], ld<T>(wrow, c), dot);
-        dot = warp_sum(dot);
+        const float dot = warp_dot<T>(xs, wrow, width, lane);
         if (lane == 0) {
             float a;
             if (kind == 0) { a = fmaxf(dot, 0.0f); a *= a; }
@@ -107,15 +151,132 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ W, const int* _
         float total = 0.0f;
         for (int k = 0; k < top; ++k) {
             const T* wrow = W + ((size_t)ids[(size_t)r * top + k] * width + n) * ff;
-            float dot = 0.0f;
-            for (int c = lane; c < ff; c += 32) dot = fmaf(as[k * ff + c], ld<T>(wrow, c), dot);
-            total = fmaf(wts[(size_t)r * top + k], warp_sum(dot), total);
+            total = fmaf(wts[(size_t)r * top + k], warp_dot<T>(as + k * ff, wrow, ff, lane), total);
         }
         if (lane == 0) y[(size_t)r * width + n] = total;
     }
 }
 
+// One block: counts per expert, offsets (exclusive prefix, [E + 1]) and each
+// pair's place in the expert-by-expert order.  Places within an expert are
+// handed out as the threads arrive; a pair's result does not depend on its place.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restrict__ offsets,
+                 int* __restrict__ place) {
+    extern __shared__ int cnt[];  // [E] counts, then [E] cursors
+    int* cursor = cnt + E;
+    pdl_prologue();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&cnt[ids[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) {
+            offsets[e] = run;
+            cursor[e] = run;
+            run += cnt[e];
+        }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) place[p] = atomicAdd(&cursor[ids[p]], 1);
+}
+
+// xg[place[p], :] = x[p / top, :]
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ place,
+                                  T* __restrict__ xg, int top, int width) {
+    pdl_prologue();
+    const int p = blockIdx.x;
+    const T* src = x + (size_t)(p / top) * width;
+    T* dst = xg + (size_t)place[p] * width;
+    const int bytes = width * (int)sizeof(T);
+    if ((bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+        for (int c = threadIdx.x; c < bytes / 16; c += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+    } else {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    }
+}
+
+template <typename T>
+__global__ void moe_activation_kernel(T* __restrict__ a, size_t n, int kind) {
+    pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = ld<T>(a, i);
+        float v;
+        if (kind == 0) { v = fmaxf(z, 0.0f); v *= v; }
+        else v = z / (1.0f + expf(-z));
+        st<T>(a, i, v);
+    }
+}
+
+// y[r, :] = sum_k wts[r, k] * yg[place[r * top + k], :], k in order
+template <typename T>
+__global__ void moe_combine_kernel(const T* __restrict__ yg, const int* __restrict__ place,
+                                   const float* __restrict__ wts, float* __restrict__ y, int top, int width) {
+    pdl_prologue();
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float total = 0.0f;
+        for (int k = 0; k < top; ++k)
+            total = fmaf(wts[(size_t)r * top + k], ld<T>(yg, (size_t)place[(size_t)r * top + k] * width + c), total);
+        y[(size_t)r * width + c] = total;
+    }
+}
+
 }  // namespace
+
+extern "C" int rfx_moe_group(const int* ids, int n_pairs, int E, int* offsets, int* place, void* stream) {
+    if (n_pairs <= 0 || E <= 0) return RFX_ERR_BAD_ARG;
+    if (E > 8192) return RFX_ERR_UNSUPPORTED;
+    RFX_LAUNCH(moe_group_kernel, 1, 1024, (size_t)2 * E * sizeof(int), (cudaStream_t)stream, ids, n_pairs, E,
+               offsets, place);
+    return 0;
+}
+
+extern "C" int rfx_moe_gather(const void* x, const int* place, void* xg, int dt, int n_pairs, int top,
+                              int width, void* stream) {
+    if (n_pairs <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(moe_gather_kernel<float>, n_pairs, 128, 0, s, (const float*)x, place, (float*)xg, top, width);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(moe_gather_kernel<__nv_bfloat16>, n_pairs, 128, 0, s, (const __nv_bfloat16*)x, place,
+                   (__nv_bfloat16*)xg, top, width);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
+
+extern "C" int rfx_moe_activation(void* a, int dt, long long n, int kind, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > sm_count() * 16) blocks = sm_count() * 16;
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(moe_activation_kernel<float>, blocks, 256, 0, s, (float*)a, (size_t)n, kind);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(moe_activation_kernel<__nv_bfloat16>, blocks, 256, 0, s, (__nv_bfloat16*)a, (size_t)n, kind);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
+
+extern "C" int rfx_moe_combine(const void* yg, int dt, const int* place, const float* wts, float* y, int R,
+                               int top, int width, void* stream) {
+    if (R <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(moe_combine_kernel<float>, R, 256, 0, s, (const float*)yg, place, wts, y, top, width);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(moe_combine_kernel<__nv_bfloat16>, R, 256, 0, s, (const __nv_bfloat16*)yg, place, wts, y, top,
+                   width);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
 
 extern "C" int rfx_moe_route(const float* logits, const float* bias, int* ids, float* wts, int R, int E,
                              int top, void* stream) {

@@ -135,11 +135,13 @@ def _env_flag(name: str, default: bool) -> bool:
 
 
 # `REFLEX_PREFILL_PROFILE=1`: CUDA events at phase marks of every eager step
-# (embed, norm, qkv_gemm, norm_rope, attn, o_proj, ffn_gate_up, ffn_down, head),
+# (embed, norm, qkv_gemm, norm_rope, attn, o_proj, ffn_gate_up, ffn_down, head, and the
+# further phases of other mixers and feed-forwards under their own names),
 # totals per phase printed to stderr after the step; a no-op when off and
 # inside graph capture (src/model/prefill_profile.rs:1-18, 26-59).
 PROFILE = _env_flag("REFLEX_PREFILL_PROFILE", False)
 _prof_events: list = []
+LAST_PROFILE: dict = {}  # phase -> ms of the last reported step, for callers that want numbers, not lines
 
 
 def prof_mark(name: str) -> None:
@@ -166,6 +168,8 @@ def prof_report(label: str) -> None:
             order.append(name)
         totals[name] += e0.elapsed_time(e1)
     whole = _prof_events[0][1].elapsed_time(_prof_events[-1][1])
+    LAST_PROFILE.clear()
+    LAST_PROFILE.update(totals, total=whole)
     for name in order:
         print(f"REFLEX_PREFILL_PROFILE step={label} phase={name} ms={totals[name]:.3f}", file=sys.stderr)
     print(f"REFLEX_PREFILL_PROFILE step={label} phase=total ms={whole:.3f}", file=sys.stderr)
@@ -825,6 +829,9 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
     R, width = x.shape
     E, ff, _w = up.shape
     top = ids.shape[1]
+    if (x.dtype == torch.bfloat16 and R > GEMV_MAX_ROWS and MOE_GROUPED
+            and not torch.cuda.is_current_stream_capturing()):
+        return moe_experts_grouped(x, up, down, ids, wts, activation)
     act = _new((R * top, ff), x.dtype, x.device)
     st = native.lib().rfx_moe_up(_chk(x, "x"), _chk(up, "up", x.dtype), _chk(ids, "ids", torch.int32),
                                  act.data_ptr(), dt_code(x.dtype), R, top, ff, width,
@@ -836,6 +843,68 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
                                    ff, width, _stream())
     native.check(st, "moe_down")
     return y
+
+
+MOE_GROUPED = _env_flag("REFLEX_B200_MOE_GROUPED", True)
+
+
+def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
+                        wts: torch.Tensor, activation: str = "relu2") -> torch.Tensor:
+    """The same sum for many bfloat16 rows (prefill): the (row, choice) pairs are
+    placed expert by expert on the device, each expert's block of rows goes
+    through its two matrices as library products (where the dense layers use
+    them too: the library's grouped product, or one product an expert where it
+    has none, for which the host reads the experts' offsets once), and a row's
+    results are summed in the order of their rank."""
+    R, width = x.shape
+    E, ff, _w = up.shape
+    top = ids.shape[1]
+    n = R * top
+    lib = native.lib()
+    offsets = _new((E + 1,), torch.int32, x.device)
+    place = _new((n,), torch.int32, x.device)
+    native.check(lib.rfx_moe_group(_chk(ids, "ids", torch.int32), n, E, offsets.data_ptr(), place.data_ptr(),
+                                   _stream()), "moe_group")
+    xg = _new((n, width), x.dtype, x.device)
+    native.check(lib.rfx_moe_gather(_chk(x, "x"), place.data_ptr(), xg.data_ptr(), dt_code(x.dtype), n, top,
+                                    width, _stream()), "moe_gather")
+    grouped = getattr(torch, "_grouped_mm", None) if _GROUPED_MM[0] else None
+    if grouped is not None and width % 8 == 0 and ff % 8 == 0:
+        # the library's grouped product reads the experts' offsets on the device: no wait for the host
+        try:
+            ends = offsets[1:]
+            act = grouped(xg, up.transpose(1, 2), offs=ends)
+            native.check(lib.rfx_moe_activation(act.data_ptr(), dt_code(act.dtype), act.numel(),
+                                                MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
+            yg = grouped(act, down.transpose(1, 2), offs=ends)
+        except (RuntimeError, TypeError, NotImplementedError):
+            _GROUPED_MM[0] = False  # this build of the library has none for these operands: one product an expert
+            yg = None
+        if yg is not None:
+            y = _new((R, width), torch.float32, x.device)
+            native.check(lib.rfx_moe_combine(_chk(yg, "yg"), dt_code(yg.dtype), place.data_ptr(),
+                                             _chk(wts, "wts", torch.float32), y.data_ptr(), R, top, width,
+                                             _stream()), "moe_combine")
+            return y
+    off = offsets.tolist()  # the one wait for the device
+    act = _new((n, ff), x.dtype, x.device)
+    for e in range(E):
+        if off[e + 1] > off[e]:
+            torch.mm(xg[off[e]:off[e + 1]], up[e].t(), out=act[off[e]:off[e + 1]])
+    native.check(lib.rfx_moe_activation(act.data_ptr(), dt_code(act.dtype), act.numel(),
+                                        MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
+    yg = _new((n, width), torch.float32, x.device)
+    for e in range(E):
+        if off[e + 1] > off[e]:
+            torch.mm(act[off[e]:off[e + 1]], down[e].t(), out_dtype=torch.float32, out=yg[off[e]:off[e + 1]])
+    y = _new((R, width), torch.float32, x.device)
+    native.check(lib.rfx_moe_combine(yg.data_ptr(), dt_code(yg.dtype), place.data_ptr(),
+                                     _chk(wts, "wts", torch.float32), y.data_ptr(), R, top, width, _stream()),
+                 "moe_combine")
+    return y
+
+
+_GROUPED_MM = [True]  # whether the library's grouped product is tried
 
 
 # ------------------------------------------------------------------ sampling

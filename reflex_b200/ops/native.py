@@ -73,6 +73,10 @@ _SIGNATURES = {
     "rfx_moe_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_moe_down": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_void_p],
+    "rfx_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "rfx_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_activation": [c_void_p, c_int, c_longlong, c_int, c_void_p],
+    "rfx_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

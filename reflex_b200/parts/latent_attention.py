@@ -97,13 +97,16 @@ class LatentAttention:
         cq, gate = ops.latent_post(proj, self.q_norm, self.kv_norm, self.eps, batch.row_pos, batch.row_slot,
                                    kv.k_pages, kv.page_table, kv.page_size, self.q_rank, self.kv_rank,
                                    H if self.has_gate else 0, ctx.writes_cache, self.dtype)
+        ops.prof_mark("latent_post")
         q = ops.linear(cq, self.q_up)
+        ops.prof_mark("q_up")
         qa = ops.heads_linear(q, self.k_absorb)  # [rows, H * kv_rank]
-        ops.prof_mark("norm_rope")
+        ops.prof_mark("q_absorb")
         attn = ops.attention(qa, kv.k_pages, kv.k_pages, kv.page_table, kv.page_size, batch, H, 1,
                              self.kv_rank, s.window, s.scale, sink=self.sink)
         ops.prof_mark("attn")
         vals = ops.heads_linear(attn, self.v_up, scale=gate if self.has_gate else None)
+        ops.prof_mark("v_up")
         if residual is not None:
             fused = ops.linear_residual(vals, self.o, residual[0], residual[1])
             if fused is not None:

@@ -83,8 +83,9 @@ class MLSTM:
         ops.prof_mark("qkv_gemm")
         num, den = ops.mlstm_scan(proj, (self.q_off, self.k_off, self.v_off, self.i_off, self.f_off),
                                   self.bias_i, self.bias_f, self.cap, s.scale, ctx.batch, ctx.state, H, d, dv)
+        ops.prof_mark("mlstm_scan")
         o = ops.mlstm_out(num, den, proj, self.g_off, self.norm, self.eps, H, dv, self.dtype)
-        ops.prof_mark("attn")
+        ops.prof_mark("mlstm_out")
         if residual is not None:
             fused = ops.linear_residual(o, self.o, residual[0], residual[1])
             if fused is not None:

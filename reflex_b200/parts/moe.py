@@ -57,7 +57,7 @@ class MixtureOfExperts:
     def forward(self, x, residual=None):
         logits = ops.linear(x, self.router, out_dtype=torch.float32)
         ids, wts = ops.moe_route(logits, self.router_bias, self.top)
-        ops.prof_mark("ffn_gate_up")
+        ops.prof_mark("moe_router")
         out = ops.moe_experts(x, self.up, self.down, ids, wts, self.activation)
-        ops.prof_mark("ffn_down")
+        ops.prof_mark("moe_experts")
         return out

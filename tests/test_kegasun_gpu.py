@@ -309,7 +309,7 @@ def test_mlstm_output_norm_and_gate(out_dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("R,E,top,ff,H", [(1, 5, 2, 24, 64), (9, 3, 3, 40, 72), (70, 8, 1, 16, 100), (5, 33, 4, 32, 128),
+@pytest.mark.parametrize("R,E,top,ff,H", [(1, 5, 2, 24, 64), (9, 3, 3, 40, 72), (70, 8, 1, 16, 100), (5, 33, 4, 32, 128), (200, 6, 2, 64, 128),
                                           (3, 40, 40, 8, 16)])
 def test_mixture_of_experts(dtype, R, E, top, ff, H):
     g = torch.Generator().manual_seed(E + top)
@@ -382,7 +382,8 @@ def check_rows(got, ref, dtype, what=""):
         assert err.max() < 2e-4, (what, int(err.argmax()), float(err.max()))
     else:
         # bfloat16 rounding moves a close router call now and then: nearly all rows are near
-        assert np.median(err) < 4e-2 and (err > 0.12).mean() <= 0.05, (what, int(err.argmax()), float(err.max()))
+        assert np.median(err) < 4e-2 and (err > 0.12).sum() <= max(1, 0.05 * len(err)), \
+            (what, int(err.argmax()), float(err.max()))
 
 
 LENGTHS = {"A": 150, "B": 300, "C": 200, "D": 280}
