@@ -113,6 +113,66 @@ heads_linear_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ W, T
     }
 }
 
+// The same product for a few rows (decode): a block takes one head's rows into
+// shared memory, a warp takes output columns one after another, reads the
+// column's weights once (16 bytes a lane where the rows allow) and applies
+// them to every row.  Sums are 32-bit; the order depends on K alone.
+constexpr int GV_ROWS = 16;
+
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+heads_gemv_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ W, TO* __restrict__ y, int ldy,
+                  const float* __restrict__ scale, int R, int N, int K, int heads) {
+    extern __shared__ __align__(16) float xs[];  // [R][K]
+    pdl_prologue();
+    const int b = blockIdx.x;
+    for (int e = threadIdx.x; e < R * K; e += blockDim.x)
+        xs[e] = ld<T>(x, (size_t)(e / K) * ldx + (size_t)b * K + e % K);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const T* wb = W + (size_t)b * N * K;
+    const bool vec = sizeof(T) == 2 && (K & 7) == 0 && (reinterpret_cast<uintptr_t>(wb) & 15) == 0;
+    for (int n = blockIdx.y * nwarps + warp; n < N; n += gridDim.y * nwarps) {
+        const T* wrow = wb + (size_t)n * K;
+        float acc[GV_ROWS];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) acc[r] = 0.0f;
+        if (vec) {
+            for (int v = lane; v < K / 8; v += 32) {
+                const uint4 u = reinterpret_cast<const uint4*>(wrow)[v];
+                const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+                float w[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(p[i]);
+                    w[2 * i] = f.x;
+                    w[2 * i + 1] = f.y;
+                }
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r) {
+                    if (r >= R) break;
+                    const float* xr = xs + r * K + 8 * v;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[r] = fmaf(xr[i], w[i], acc[r]);
+                }
+            }
+        } else {
+            for (int c = lane; c < K; c += 32) {
+                const float w = ld<T>(wrow, c);
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; ++r)
+                    if (r < R) acc[r] = fmaf(xs[r * K + c], w, acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; ++r) {
+            if (r >= R) break;
+            const float v = warp_sum(acc[r]);
+            if (lane == 0) st<TO>(y + (size_t)r * ldy + (size_t)b * N, n, v * (scale ? scale[(size_t)r * heads + b] : 1.0f));
+        }
+    }
+}
+
 // y[r, b, :] *= scale[r, b]
 template <typename T>
 __global__ void scale_heads_kernel(T* __restrict__ y, const float* __restrict__ scale, size_t total,
@@ -149,9 +209,26 @@ extern "C" int rfx_heads_linear(const void* x, int ldx, const void* W, void* y, 
                                 const float* scale, int R, int N, int K, int heads, void* stream) {
     if (R <= 0 || N <= 0 || heads <= 0) return 0;
     if (K <= 0) return RFX_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (R <= GV_ROWS && (size_t)R * K * sizeof(float) <= 48 * 1024) {
+        // a few rows: every weight is read once and meets all rows
+        int gy = (N + 7) / 8;
+        if (gy > 32) gy = 32;
+        dim3 g(heads, gy);
+        const size_t smem = (size_t)R * K * sizeof(float);
+        if (dt == RFX_DT_F32)
+            RFX_LAUNCH((heads_gemv_kernel<float, float>), g, 256, smem, s, (const float*)x, ldx, (const float*)W,
+                       (float*)y, ldy, scale, R, N, K, heads);
+        else if (dt == RFX_DT_BF16)
+            RFX_LAUNCH((heads_gemv_kernel<__nv_bfloat16, __nv_bfloat16>), g, 256, smem, s,
+                       (const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)W, (__nv_bfloat16*)y, ldy, scale, R, N,
+                       K, heads);
+        else
+            return RFX_ERR_BAD_ARG;
+        return 0;
+    }
     dim3 grid((N + TN - 1) / TN, (R + TM - 1) / TM, heads);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
-    cudaStream_t s = (cudaStream_t)stream;
     if (dt == RFX_DT_F32)
         RFX_LAUNCH((heads_linear_kernel<float, float>), grid, 256, 0, s, (const float*)x, ldx,
                    (const float*)W, (float*)y, ldy, scale, R, N, K, heads);
