@@ -829,9 +829,10 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
     R, width = x.shape
     E, ff, _w = up.shape
     top = ids.shape[1]
-    if (x.dtype == torch.bfloat16 and R > GEMV_MAX_ROWS and MOE_GROUPED
-            and not torch.cuda.is_current_stream_capturing()):
-        return moe_experts_grouped(x, up, down, ids, wts, activation)
+    if x.dtype == torch.bfloat16 and MOE_GROUPED and R >= MOE_GROUPED_MIN_ROWS:
+        # captured steps too, as long as the library's grouped product (no wait for the host) is there
+        if not torch.cuda.is_current_stream_capturing() or (_GROUPED_MM[0] and width % 8 == 0 and ff % 8 == 0):
+            return moe_experts_grouped(x, up, down, ids, wts, activation)
     act = _new((R * top, ff), x.dtype, x.device)
     st = native.lib().rfx_moe_up(_chk(x, "x"), _chk(up, "up", x.dtype), _chk(ids, "ids", torch.int32),
                                  act.data_ptr(), dt_code(x.dtype), R, top, ff, width,
@@ -846,6 +847,10 @@ def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
 
 
 MOE_GROUPED = _env_flag("REFLEX_B200_MOE_GROUPED", True)
+# From two rows on, experts are likely shared between rows, and the grouped form reads each
+# expert's matrices once (measured at batch 8 with 16 experts, 4 chosen: a decode step 1.41 ->
+# 1.05 ms at width 2048); one row streams its own experts directly.
+MOE_GROUPED_MIN_ROWS = _env_int("REFLEX_B200_MOE_GROUPED_MIN_ROWS", 2, 1, 1 << 30)
 
 
 def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
@@ -876,7 +881,13 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
             act = grouped(xg, up.transpose(1, 2), offs=ends)
             native.check(lib.rfx_moe_activation(act.data_ptr(), dt_code(act.dtype), act.numel(),
                                                 MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
-            yg = grouped(act, down.transpose(1, 2), offs=ends)
+            try:  # 32-bit results where the library gives them: the weighted sum then rounds once
+                yg = grouped(act, down.transpose(1, 2), offs=ends, out_dtype=torch.float32) if _GROUPED_MM[1] else None
+            except (RuntimeError, TypeError, NotImplementedError):
+                _GROUPED_MM[1] = False
+                yg = None
+            if yg is None:
+                yg = grouped(act, down.transpose(1, 2), offs=ends)
         except (RuntimeError, TypeError, NotImplementedError):
             _GROUPED_MM[0] = False  # this build of the library has none for these operands: one product an expert
             yg = None
@@ -904,7 +915,7 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
     return y
 
 
-_GROUPED_MM = [True]  # whether the library's grouped product is tried
+_GROUPED_MM = [True, True]  # whether the library's grouped product is tried, and its 32-bit output
 
 
 # ------------------------------------------------------------------ sampling

@@ -71,7 +71,23 @@ KEG_D = model(200, 128, 1e-5, 3.0, (211, 5, 9), [
     (mlstm(4, 32, 32, 10.0), dense(256)),
 ])
 
-ALL = {"A": KEG_A, "B": KEG_B, "C": KEG_C, "D": KEG_D}
+# E: awkward sizes throughout: five heads of 10, values of 6, a latent of 48, a window of 33,
+# an mLSTM whose values are no multiple of four and span two column slices, one expert
+# of one, a dense width that is no multiple of 8
+KEG_E = model(77, 88, 1e-5, 1.5, (19, 3, 5), [
+    (latent(5, 10, 6, 12, 48, 33, 0.31), moe(1, 1, 20)),
+    (mlstm(3, 10, 70, 6.0), dense(36)),
+    (latent(5, 10, 6, 12, 48, 33, 0.31), dense(36)),
+])
+# F: a latent of 192 (three 64-column boxes), key sizes of 200 and 300 in the mLSTM (the
+# widest register form, and the shared-memory form), a window longer than the prompts
+KEG_F = model(90, 96, 1e-5, 2.5, (64, 9, 1), [
+    (mlstm(2, 200, 16, 9.0), None),
+    (latent(2, 64, 32, 48, 192, 1000, 0.125), moe(4, 2, 48)),
+    (mlstm(1, 300, 8, 20.0), dense(64)),
+])
+
+ALL = {"A": KEG_A, "B": KEG_B, "C": KEG_C, "D": KEG_D, "E": KEG_E, "F": KEG_F}
 
 # tensor-name suffix -> factor
 SHARP = (("mix.uq", 14.0), ("mix.uk", 14.0), ("mix.sink", 5.0), ("mix.i", 25.0), ("mix.f", 25.0),
