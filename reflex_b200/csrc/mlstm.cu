@@ -263,6 +263,277 @@ mlstm_scan_reg_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
     if (tid == 0) st_h[(size_t)dim * vdim + dim + blockIdx.z] = m;
 }
 
+// The chunkwise form for many rows a sequence (prefill).  With F_t the sum of
+// the log forget gates from the chunk's first row to t, g_s = i_s - F_s and
+// M_t = max(m_prev, max_{s<=t} g_s), the walk above gives m_t = F_t + M_t and
+//   S_t^T q_t = e^(m_prev - M_t) S_prev^T q_t + sum_{s<=t} e^(g_s - M_t) (q_t . k_s) v_s
+//   S_L = e^(m_prev - M_L) S_prev + sum_s e^(g_s - M_L) k_s v_s^T
+// (every exponent is <= 0), and the same for n with v = 1.  A block owns
+// (sequence, head, 64 value columns) and takes 32 rows at a time: the gates'
+// sums and maxima by one warp's shuffles, then three small 32-bit products in
+// registers over shared-memory tiles (the rows' scores, the read-out, the
+// state's update).  dim <= 16 RD.  The rows' q, k, v and gate pre-activations
+// arrive by 4-byte asynchronous copies, with NB = 2 a chunk ahead of their use.
+template <int RD, int NB>
+__global__ void __launch_bounds__(256)
+mlstm_chunk_kernel(const float* __restrict__ proj, int ld, int q_off, int k_off, int v_off, int i_off,
+                   int f_off, const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
+                   float q_scale, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                   float* __restrict__ state, float* __restrict__ num, float* __restrict__ den, int heads,
+                   int dim, int vdim) {
+    constexpr int L = 32, DMAX = 16 * RD, DP = DMAX + 4, VP = VT + 4, LP = L + 1;
+    extern __shared__ __align__(16) float smem[];
+    constexpr int TILE = 2 * L * DP + L * VP + 2 * L;  // q, k, v and the two gates of a chunk
+    float* Ss = smem + NB * TILE;   // [DMAX][VP]
+    float* ns = Ss + DMAX * VP;     // [DMAX]
+    float* Ps = ns + DMAX;          // [L][LP]
+    float* Fs = Ps + L * LP;        // [L] each: F, g, M, e^(m_prev - M), e^(g - M_L)
+    float* gs = Fs + L;
+    float* Ms = gs + L;
+    float* dec = Ms + L;
+    float* wl = dec + L;
+    float* two = wl + L;            // e^(m_prev - M_L), m_L
+    pdl_prologue();
+    const int seq = blockIdx.x, h = blockIdx.y;
+    const int j0 = blockIdx.z * VT;
+    const int nv = min(VT, vdim - j0);
+    const bool has_n = blockIdx.z == 0;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int cg = tid & 15, rp = tid >> 4;
+    const int slot = seq_slot[seq];
+    const int row0 = seq_row0[seq], n_rows = seq_row0[seq + 1] - row0;
+    const size_t per_head = (size_t)dim * vdim + dim + gridDim.z;
+    float* st_h = state + ((size_t)slot * heads + h) * per_head;
+    const float bi = bias_i[h], bf = bias_f[h];
+
+    for (int e = tid; e < NB * TILE; e += 256) smem[e] = 0.0f;  // what no copy writes stays zero
+    for (int e = tid; e < DMAX * VT; e += 256) {
+        const int d = e / VT, j = e % VT;
+        Ss[d * VP + j] = (d < dim && j < nv) ? st_h[(size_t)d * vdim + j0 + j] : 0.0f;
+    }
+    __syncthreads();
+    auto issue = [&](int buf, int t0) {
+        float* base = smem + buf * TILE;
+        const int nt = min(L, n_rows - t0);
+        for (int e = tid; e < nt * dim; e += 256) {
+            const int t = e / dim, d = e % dim;
+            const float* row = proj + (size_t)(row0 + t0 + t) * ld;
+            cp_async4(base + t * DP + d, row + q_off + h * dim + d);
+            cp_async4(base + L * DP + t * DP + d, row + k_off + h * dim + d);
+        }
+        for (int e = tid; e < nt * nv; e += 256) {
+            const int t = e / nv, j = e % nv;
+            cp_async4(base + 2 * L * DP + t * VP + j, proj + (size_t)(row0 + t0 + t) * ld + v_off + h * vdim + j0 + j);
+        }
+        for (int t = tid; t < nt; t += 256) {
+            const float* row = proj + (size_t)(row0 + t0 + t) * ld;
+            cp_async4(base + 2 * L * DP + L * VP + t, row + i_off + h);
+            cp_async4(base + 2 * L * DP + L * VP + L + t, row + f_off + h);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (NB == 2 && n_rows > 0) issue(0, 0);
+    for (int d = tid; d < DMAX; d += 256) ns[d] = d < dim ? st_h[(size_t)dim * vdim + d] : 0.0f;
+    float m_prev = st_h[(size_t)dim * vdim + dim + blockIdx.z];
+
+    for (int t0 = 0, buf = 0; t0 < n_rows; t0 += L, buf = (buf + 1) % NB) {
+        const int nt = min(L, n_rows - t0);
+        __syncthreads();  // the chunk before is done with the tiles
+        if (NB == 2) {
+            if (t0 + L < n_rows) {
+                issue(buf ^ 1, t0 + L);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+        } else {
+            issue(0, t0);
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        // rows beyond the chunk's may hold an earlier chunk's values: nothing below reads
+        // them into a result (their weights are zero, their scores masked, their sums not stored)
+        const float* Qs = smem + buf * TILE;  // [L][DP], unscaled: the results take q's scale
+        const float* Ks = Qs + L * DP;        // [L][DP]
+        const float* Vs = Ks + L * DP;        // [L][VP]
+        const float* raw = Vs + L * VP;       // [2][L]
+        if (tid < L) {  // one warp: the gates, their running sum and running maximum
+            float gi = -INFINITY, F = 0.0f;
+            if (lane < nt) {
+                gi = cap * tanhf((raw[lane] + bi) / cap);
+                F = log_sigmoid(cap * tanhf((raw[L + lane] + bf) / cap));
+            }
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float v = __shfl_up_sync(0xffffffffu, F, o);
+                if (lane >= o) F += v;
+            }
+            const float g = gi - F;  // -inf beyond the chunk's rows
+            float M = fmaxf(g, m_prev);
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float v = __shfl_up_sync(0xffffffffu, M, o);
+                if (lane >= o) M = fmaxf(M, v);
+            }
+            const float ML = __shfl_sync(0xffffffffu, M, nt - 1), FL = __shfl_sync(0xffffffffu, F, nt - 1);
+            Fs[lane] = F;
+            gs[lane] = g;
+            Ms[lane] = M;
+            dec[lane] = expf(m_prev - M);
+            wl[lane] = expf(g - ML);
+            if (lane == 0) {
+                two[0] = expf(m_prev - ML);
+                two[1] = FL + ML;
+            }
+        }
+        __syncthreads();
+        {   // scores of row t against rows s <= t, times their weights
+            const int t = tid >> 3, si = tid & 7;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            const float4* q4 = reinterpret_cast<const float4*>(Qs + t * DP);
+#pragma unroll 4
+            for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+                const float4 q = q4[d4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float4 k = reinterpret_cast<const float4*>(Ks + (si + 8 * j) * DP)[d4];
+                    acc[j] = fmaf(q.x, k.x, acc[j]);
+                    acc[j] = fmaf(q.y, k.y, acc[j]);
+                    acc[j] = fmaf(q.z, k.z, acc[j]);
+                    acc[j] = fmaf(q.w, k.w, acc[j]);
+                }
+            }
+            const float Mt = Ms[t];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int sidx = si + 8 * j;
+                Ps[t * LP + sidx] = sidx <= t ? acc[j] * expf(gs[sidx] - Mt) : 0.0f;
+            }
+        }
+        __syncthreads();
+        {   // read-out: rows 2 rp and 2 rp + 1, columns 4 cg .. 4 cg + 3
+            float acc[2][4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = 0.0f;
+            const float4* qa = reinterpret_cast<const float4*>(Qs + (2 * rp) * DP);
+            const float4* qb = reinterpret_cast<const float4*>(Qs + (2 * rp + 1) * DP);
+#pragma unroll 2
+            for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+                const float4 a = qa[d4], b = qb[d4];
+                const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 sv = *reinterpret_cast<const float4*>(Ss + (4 * d4 + i) * VP + 4 * cg);
+                    acc[0][0] = fmaf(av[i], sv.x, acc[0][0]);
+                    acc[0][1] = fmaf(av[i], sv.y, acc[0][1]);
+                    acc[0][2] = fmaf(av[i], sv.z, acc[0][2]);
+                    acc[0][3] = fmaf(av[i], sv.w, acc[0][3]);
+                    acc[1][0] = fmaf(bv[i], sv.x, acc[1][0]);
+                    acc[1][1] = fmaf(bv[i], sv.y, acc[1][1]);
+                    acc[1][2] = fmaf(bv[i], sv.z, acc[1][2]);
+                    acc[1][3] = fmaf(bv[i], sv.w, acc[1][3]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const float dt = dec[2 * rp + r];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] *= dt;
+            }
+            for (int sidx = 0; sidx <= 2 * rp + 1; ++sidx) {
+                const float4 v = *reinterpret_cast<const float4*>(Vs + sidx * VP + 4 * cg);
+                const float pa = Ps[(2 * rp) * LP + sidx], pb = Ps[(2 * rp + 1) * LP + sidx];
+                acc[0][0] = fmaf(pa, v.x, acc[0][0]);
+                acc[0][1] = fmaf(pa, v.y, acc[0][1]);
+                acc[0][2] = fmaf(pa, v.z, acc[0][2]);
+                acc[0][3] = fmaf(pa, v.w, acc[0][3]);
+                acc[1][0] = fmaf(pb, v.x, acc[1][0]);
+                acc[1][1] = fmaf(pb, v.y, acc[1][1]);
+                acc[1][2] = fmaf(pb, v.z, acc[1][2]);
+                acc[1][3] = fmaf(pb, v.w, acc[1][3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int t = 2 * rp + r;
+                if (t < nt) {
+                    float* dst = num + ((size_t)(row0 + t0 + t) * heads + h) * vdim + j0 + 4 * cg;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (4 * cg + c < nv) dst[c] = acc[r][c] * q_scale;
+                }
+            }
+        }
+        if (has_n) {  // n . q: eight lanes a row
+            const int t = tid >> 3, l8 = tid & 7;
+            float qn = 0.0f, ps = 0.0f;
+            for (int d = l8; d < DMAX; d += 8) qn = fmaf(Qs[t * DP + d], ns[d], qn);
+            for (int sidx = l8; sidx < L; sidx += 8) ps += Ps[t * LP + sidx];
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                qn += __shfl_xor_sync(0xffffffffu, qn, o);
+                ps += __shfl_xor_sync(0xffffffffu, ps, o);
+            }
+            if (l8 == 0 && t < nt)
+                den[(size_t)(row0 + t0 + t) * heads + h] =
+                    fmaxf(fabsf(fmaf(dec[t], qn, ps) * q_scale), expf(-(Fs[t] + Ms[t]))) + 1e-6f;
+        }
+        __syncthreads();  // every read of S and n is done
+        {   // the state: rows rp RD .. + RD - 1 of S, columns 4 cg .. + 3
+            const float dl = two[0];
+            float acc[RD][4];
+#pragma unroll
+            for (int i = 0; i < RD; ++i) {
+                const float4 sv = *reinterpret_cast<const float4*>(Ss + (rp * RD + i) * VP + 4 * cg);
+                acc[i][0] = dl * sv.x;
+                acc[i][1] = dl * sv.y;
+                acc[i][2] = dl * sv.z;
+                acc[i][3] = dl * sv.w;
+            }
+            for (int sidx = 0; sidx < nt; ++sidx) {
+                const float w = wl[sidx];
+                float4 v = *reinterpret_cast<const float4*>(Vs + sidx * VP + 4 * cg);
+                v.x *= w;
+                v.y *= w;
+                v.z *= w;
+                v.w *= w;
+                const float4* k4 = reinterpret_cast<const float4*>(Ks + sidx * DP + rp * RD);
+#pragma unroll
+                for (int i4 = 0; i4 < RD / 4; ++i4) {
+                    const float4 k = k4[i4];
+                    const float kv[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        acc[4 * i4 + i][0] = fmaf(kv[i], v.x, acc[4 * i4 + i][0]);
+                        acc[4 * i4 + i][1] = fmaf(kv[i], v.y, acc[4 * i4 + i][1]);
+                        acc[4 * i4 + i][2] = fmaf(kv[i], v.z, acc[4 * i4 + i][2]);
+                        acc[4 * i4 + i][3] = fmaf(kv[i], v.w, acc[4 * i4 + i][3]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < RD; ++i)
+                *reinterpret_cast<float4*>(Ss + (rp * RD + i) * VP + 4 * cg) =
+                    make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            for (int d = tid; d < DMAX; d += 256) {
+                float a = dl * ns[d];
+                for (int sidx = 0; sidx < nt; ++sidx) a = fmaf(wl[sidx], Ks[sidx * DP + d], a);
+                ns[d] = a;
+            }
+            m_prev = two[1];
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < dim * nv; e += 256) {
+        const int d = e / nv, j = e % nv;
+        st_h[(size_t)d * vdim + j0 + j] = Ss[d * VP + j];
+    }
+    if (has_n)
+        for (int d = tid; d < dim; d += 256) st_h[(size_t)dim * vdim + d] = ns[d];
+    if (tid == 0) st_h[(size_t)dim * vdim + dim + blockIdx.z] = m_prev;
+}
+
 // One warp per (row, head).
 template <typename TO>
 __global__ void mlstm_out_kernel(const float* __restrict__ num, const float* __restrict__ den,
@@ -335,6 +606,36 @@ extern "C" int rfx_mlstm_scan(const float* proj, int ld, int q_off, int k_off, i
                i_off, f_off, bias_i, bias_f, cap, q_scale, seq_slot, seq_row0, state, num, den, heads, dim,
                vdim);
     return 0;
+}
+
+// The chunkwise form (many rows a sequence); RFX_ERR_UNSUPPORTED beyond dim 256.
+extern "C" int rfx_mlstm_chunk(const float* proj, int ld, int q_off, int k_off, int v_off, int i_off,
+                               int f_off, const float* bias_i, const float* bias_f, float cap,
+                               float q_scale, const int* seq_slot, const int* seq_row0, int S,
+                               float* state, float* num, float* den, int heads, int dim, int vdim,
+                               void* stream) {
+    if (S <= 0) return 0;
+    if (heads <= 0 || dim <= 0 || vdim <= 0 || cap <= 0.0f) return RFX_ERR_BAD_ARG;
+    if (dim > 256) return RFX_ERR_UNSUPPORTED;
+    dim3 grid(S, heads, (vdim + VT - 1) / VT);
+    if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
+#define RFX_CHUNK(RD, NB)                                                                                   \
+    do {                                                                                                    \
+        constexpr int L = 32, DMAX = 16 * RD, DP = DMAX + 4, VP = VT + 4, LP = L + 1;                       \
+        const size_t sm = ((size_t)NB * (2 * L * DP + L * VP + 2 * L) + DMAX * VP + DMAX + L * LP + 5 * L + 2) * \
+                          sizeof(float);                                                                    \
+        cudaError_t e = cudaFuncSetAttribute((mlstm_chunk_kernel<RD, NB>),                                  \
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);         \
+        if (e != cudaSuccess) return (int)e;                                                                \
+        RFX_LAUNCH((mlstm_chunk_kernel<RD, NB>), grid, 256, sm, (cudaStream_t)stream, proj, ld, q_off, k_off, \
+                   v_off, i_off, f_off, bias_i, bias_f, cap, q_scale, seq_slot, seq_row0, state, num, den,  \
+                   heads, dim, vdim);                                                                       \
+        return 0;                                                                                           \
+    } while (0)
+    if (dim <= 64) RFX_CHUNK(4, 2);
+    if (dim <= 128) RFX_CHUNK(8, 2);
+    RFX_CHUNK(16, 1);  // two chunks of 256-wide rows beside the state do not fit shared memory
+#undef RFX_CHUNK
 }
 
 extern "C" int rfx_mlstm_out(const float* num, const float* den, const float* proj, int ld, int g_off,

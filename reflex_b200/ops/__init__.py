@@ -767,12 +767,18 @@ def mlstm_state_floats(dim: int, vdim: int) -> int:
     return dim * vdim + dim + (vdim + MLSTM_SLICE - 1) // MLSTM_SLICE
 
 
+MLSTM_CHUNK_MIN_ROWS = _env_int("REFLEX_B200_MLSTM_CHUNK_MIN_ROWS", 48, 1, 1 << 30)
+
+
 def mlstm_scan(proj: torch.Tensor, offsets, bias_i, bias_f, cap: float, q_scale: float, batch,
-               state: torch.Tensor, heads: int, dim: int, vdim: int):
+               state: torch.Tensor, heads: int, dim: int, vdim: int, max_rows: Optional[int] = None):
     """The recurrence over the step's rows, sequence by sequence.  `proj`
     float32 [R, ld] holds q, k, v and the two gate pre-activations at the
     column offsets `offsets` = (q, k, v, i, f); `state` [slots, heads, floats].
-    Returns the numerators S^T q [R, heads * vdim] and denominators [R, heads]."""
+    Returns the numerators S^T q [R, heads * vdim] and denominators [R, heads].
+    `max_rows`: the most rows any sequence brings; from `MLSTM_CHUNK_MIN_ROWS`
+    on (and dim up to 256) the chunkwise kernel runs, else the row-by-row walk:
+    the same function, rounded differently."""
     R = proj.shape[0]
     _chk(proj, "proj", torch.float32)
     if state.shape[-1] != mlstm_state_floats(dim, vdim) or state.shape[-2] != heads:
@@ -780,7 +786,9 @@ def mlstm_scan(proj: torch.Tensor, offsets, bias_i, bias_f, cap: float, q_scale:
     num = _new((R, heads * vdim), torch.float32, proj.device)
     den = _new((R, heads), torch.float32, proj.device)
     q_off, k_off, v_off, i_off, f_off = (int(o) for o in offsets)
-    st = native.lib().rfx_mlstm_scan(
+    chunked = max_rows is not None and max_rows >= MLSTM_CHUNK_MIN_ROWS and dim <= 256
+    fn = native.lib().rfx_mlstm_chunk if chunked else native.lib().rfx_mlstm_scan
+    st = fn(
         proj.data_ptr(), proj.shape[1], q_off, k_off, v_off, i_off, f_off,
         _chk(bias_i, "bias_i", torch.float32), _chk(bias_f, "bias_f", torch.float32), float(cap),
         float(q_scale), _chk(batch.seq_slot, "seq_slot", torch.int32),

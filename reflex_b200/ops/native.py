@@ -67,6 +67,9 @@ _SIGNATURES = {
     "rfx_mlstm_scan": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
                        c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                        c_void_p],
+    "rfx_mlstm_chunk": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                        c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                        c_void_p],
     "rfx_mlstm_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
                       c_int, c_int, c_void_p],
     "rfx_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],

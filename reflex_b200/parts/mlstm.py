@@ -82,7 +82,8 @@ class MLSTM:
         proj = ops.linear(x, self.stacked, out_dtype=torch.float32)
         ops.prof_mark("qkv_gemm")
         num, den = ops.mlstm_scan(proj, (self.q_off, self.k_off, self.v_off, self.i_off, self.f_off),
-                                  self.bias_i, self.bias_f, self.cap, s.scale, ctx.batch, ctx.state, H, d, dv)
+                                  self.bias_i, self.bias_f, self.cap, s.scale, ctx.batch, ctx.state, H, d, dv,
+                                  max_rows=ctx.batch.max_new)
         ops.prof_mark("mlstm_scan")
         o = ops.mlstm_out(num, den, proj, self.g_off, self.norm, self.eps, H, dv, self.dtype)
         ops.prof_mark("mlstm_out")

@@ -238,8 +238,10 @@ def _mlstm_ref(q, k, v, ia, fa, cap):
     return np.stack(num), np.array(den)
 
 
-@pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 16, 40, 8.0), (1, 24, 130, 15.0), (3, 8, 8, 5.0), (2, 100, 64, 12.0)])
-def test_mlstm_recurrence_carried_through_its_state(heads, dim, vdim, cap):
+@pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("heads,dim,vdim,cap", [(2, 16, 40, 8.0), (1, 24, 130, 15.0), (3, 8, 8, 5.0), (2, 100, 64, 12.0),
+                                                (1, 200, 20, 9.0)])
+def test_mlstm_recurrence_carried_through_its_state(heads, dim, vdim, cap, chunked):
     """Three sequences of unequal lengths, cut into steps of unequal sizes (down
     to one row) in slots that are not in order: every step goes on from the
     state the step before left; a slot taken again starts from zero."""
@@ -263,8 +265,9 @@ def test_mlstm_recurrence_carried_through_its_state(heads, dim, vdim, cap):
         ids = list(cuts)
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [fed[s] for s in ids])
         rows = torch.cat([proj[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV)
+        # the chunkwise kernel (chunks of 32 rows: whole, partial and single-row chunks) or the walk
         num, den = ops().mlstm_scan(rows, (q_off, k_off, v_off, i_off, f_off), bi.to(DEV), bf.to(DEV), cap, 0.25,
-                                    b, state, heads, dim, vdim)
+                                    b, state, heads, dim, vdim, max_rows=10 ** 6 if chunked else None)
         for j, s in enumerate(ids):
             got_num[s].append(num[b.row0[j]:b.row0[j + 1]].cpu())
             got_den[s].append(den[b.row0[j]:b.row0[j + 1]].cpu())
@@ -289,7 +292,7 @@ def test_mlstm_recurrence_carried_through_its_state(heads, dim, vdim, cap):
     state[0].zero_()
     b = FakeBatch([[0] * 9], [0], [0])
     num, den = ops().mlstm_scan(proj[1].to(DEV), (q_off, k_off, v_off, i_off, f_off), bi.to(DEV), bf.to(DEV), cap,
-                                0.25, b, state, heads, dim, vdim)
+                                0.25, b, state, heads, dim, vdim, max_rows=10 ** 6 if chunked else None)
     check(1, num.cpu(), den.cpu())
 
 
