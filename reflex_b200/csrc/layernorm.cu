@@ -1,6 +1,6 @@
 // Layer norm with a weight and no bias, with the residual add that precedes it.
 //
-// One block per output row, the same contract as the RMSNorm kernel:
+// One block per output row, the same interface as the RMSNorm kernel:
 //   src = rows ? rows[blockIdx.x] : blockIdx.x
 //   t   = x[src] (+ delta[src])                     residual sum in 32-bit
 //   if x_out: x_out[src] = t                        (only without `rows`; may be x)
