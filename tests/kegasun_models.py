@@ -87,7 +87,13 @@ KEG_F = model(90, 96, 1e-5, 2.5, (64, 9, 1), [
     (mlstm(1, 300, 8, 20.0), dense(64)),
 ])
 
-ALL = {"A": KEG_A, "B": KEG_B, "C": KEG_C, "D": KEG_D, "E": KEG_E, "F": KEG_F}
+# G: no attention at all (the cache then holds state only)
+KEG_G = model(50, 48, 1e-5, 1.0, (31, 2, 3), [
+    (mlstm(2, 12, 24, 7.0), moe(4, 2, 16)),
+    (mlstm(3, 16, 16, 11.0), None),
+])
+
+ALL = {"A": KEG_A, "B": KEG_B, "C": KEG_C, "D": KEG_D, "E": KEG_E, "F": KEG_F, "G": KEG_G}
 
 # tensor-name suffix -> factor
 SHARP = (("mix.uq", 14.0), ("mix.uk", 14.0), ("mix.sink", 5.0), ("mix.i", 25.0), ("mix.f", 25.0),
