@@ -182,7 +182,10 @@ class StateGroup:
 
 
 class Cache:
-    """`entry_specs`: cache entry id -> KVSpec | StateSpec | None."""
+    """`entry_specs`: cache entry id -> KVSpec | StateSpec | None, or a tuple of
+    them for a mixer that keeps several things (keys and values and a state; two
+    states): its parts are stored like entries of their own, under (entry, i),
+    and `views(entry)` hands them out in the tuple's order."""
 
     def __init__(self, entry_specs: Dict[int, Union[KVSpec, StateSpec, None]], max_tokens: int,
                  max_positions: int, dtype: torch.dtype, device, max_slots: Optional[int] = None):
@@ -201,9 +204,15 @@ class Cache:
         self.state_groups: List[StateGroup] = []
         self._where: Dict[int, Tuple[str, int]] = {}
         by_spec: Dict[Union[KVSpec, StateSpec], List[int]] = {}
+        self._parts: Dict[int, List[Tuple[int, int]]] = {}
         for entry in sorted(entry_specs):
             spec = entry_specs[entry]
             if spec is None:
+                continue
+            if isinstance(spec, (tuple, list)):
+                self._parts[entry] = [(entry, i) for i in range(len(spec))]
+                for key, part in zip(self._parts[entry], spec):
+                    by_spec.setdefault(part, []).append(key)
                 continue
             by_spec.setdefault(spec, []).append(entry)
         for spec, entries in by_spec.items():
@@ -306,7 +315,18 @@ class Cache:
         return self.state_groups[gi].view(entry)
 
     def has(self, entry: int) -> Optional[str]:
+        """"kv", "state", "parts" (a tuple of them: `views`), or None."""
+        if entry in self._parts:
+            return "parts"
         return self._where.get(entry, (None, 0))[0]
+
+    def views(self, entry: int) -> list:
+        """The parts of an entry whose mixer asked for a tuple, in its order: a
+        `KVView` for each `KVSpec`, a [slots, *shape] tensor for each `StateSpec`."""
+        out = []
+        for key in self._parts[entry]:
+            out.append(self.kv(key) if self._where[key][0] == "kv" else self.state(key))
+        return out
 
     def tokens_held(self) -> int:
         """Most pages any group holds, in tokens."""

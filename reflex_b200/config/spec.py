@@ -61,7 +61,9 @@ class MixerSpec:
     position: Optional[PositionSpec] = None
     names: Tuple[Tuple[str, str], ...] = ()
     # what only some kinds have, by name: "latent_attention" reads q_rank, kv_rank,
-    # eps and sink; "mlstm" reads gate_cap and eps
+    # eps and sink; "mlstm" reads gate_cap and eps; "conv_attention" reads kv taps,
+    # temp_coef, temp_every, sink and distance_slopes; "rglru" reads width, blocks,
+    # taps and decay_scale; "pair" reads left and right (two `MixerSpec`s) and eps
     params: Tuple[Tuple[str, Any], ...] = ()
     # size of a head's value vector when it differs from `head_dim`; 0: the same
     v_head_dim: int = 0
@@ -76,7 +78,8 @@ class MixerSpec:
 
 @dataclass(frozen=True)
 class FeedForwardSpec:
-    kind: str  # "swiglu"; "moe" (params: experts, top, activation, router_bias)
+    kind: str  # "swiglu"; "glu_clamped" (params: alpha, limit); "moe" (params: experts, top, activation,
+    # router_bias, scores, weight_input, alpha, limit, shared_ff, shared_limit)
     hidden_size: int
     intermediate_size: int
     names: Tuple[Tuple[str, str], ...] = ()
@@ -136,6 +139,9 @@ class RunEntry:
     layer: int
     cache: int
     writes_cache: bool = True
+    # the run starts from a mix of the stream and the embedding output x0,
+    # x <- W [x; x0] with the model's `stream_mix_name` matrix [hidden, 2 hidden]
+    mixes_input: bool = False
 
 
 @dataclass
@@ -159,6 +165,11 @@ class ModelSpec:
     eos_token_ids: Tuple[int, ...] = ()
     # terms added to the token embedding, in order
     embedding_terms: Tuple[EmbeddingTermSpec, ...] = ()
+    # logits <- cap * tanh(logits / cap) after the scale; 0: no cap
+    logit_softcap: float = 0.0
+    # the matrix of the runs that start from a mix of the stream and the embedding
+    # output (`RunEntry.mixes_input`); None: the model has none
+    stream_mix_name: Optional[str] = None
 
     def __post_init__(self) -> None:
         if not self.run_order:

@@ -86,8 +86,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                         const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ partial, int nq,
                         int n_htiles, int n_splits, int window, float scale_log2,
-                        const float* __restrict__ sink, int cluster_merge, int trace_id,
-                        int* __restrict__ err) {
+                        const float* __restrict__ sink, const float* __restrict__ slopes,
+                        int cluster_merge, int trace_id, int* __restrict__ err) {
     constexpr int LD = D + 8;
     constexpr int TILE = TMA ? PAGE * D : PAGE * LD;  // elements of a page's key (or value) tile
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -160,6 +160,14 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 
     // this thread's heads are 2 (lane % 4) and 2 (lane % 4) + 1 (attn_mma.cuh: attend_keys16)
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    // a distance bias: slope * (query position - key position) off every score; the
+    // slopes are weights (no kernel writes them), times log2(e) like the scale
+    float pen[2] = {0.0f, 0.0f};
+    if (slopes) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (2 * (lane & 3) + j < nh) pen[j] = slopes[h0 + 2 * (lane & 3) + j] * LOG2E;
+    }
     float acc[D / 16][4];
 #pragma unroll
     for (int n = 0; n < D / 16; ++n)
@@ -208,7 +216,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         if (warp < 4) {
             auto nothing = [&](int) { return false; };
             attend_keys16<D, true>(qf, kbuf + (DEC_STAGES - 1) * TILE, vbuf + (DEC_STAGES - 1) * TILE, warp * 16,
-                                   scale_log2, nothing, m, l, acc);
+                                   scale_log2, nothing, pen, 0, m, l, acc);
             reset();
             // the dry pass is this buffer's first use: done with it
             __syncwarp();
@@ -272,8 +280,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (tracing) waited += c2 - c0;
                 const int base = pg * PAGE;
                 auto visible = [&](int key) { return base + key >= lo && base + key <= pos; };
-                attend_keys16<D, true>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible, m,
-                                       l, acc);
+                attend_keys16<D, true>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
+                                       pen, pos - base, m, l, acc);
                 __syncwarp();
                 if (lane == 0) sm100::mbar_arrive(&empty_bar[buf]);
                 if (tracing) attending += clock64() - c2;
@@ -302,8 +310,8 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int base = pg * PAGE;
             const int lo_eff = dry ? 0x7fffffff : lo;
             auto visible = [&](int key) { return base + key >= lo_eff && base + key <= pos; };
-            attend_keys16<D, false>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible, m, l,
-                                    acc);
+            attend_keys16<D, false>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
+                                    pen, pos - base, m, l, acc);
             if (tracing && !dry) attending += clock64() - c2;
             if (dry) {
                 reset();
@@ -524,8 +532,8 @@ const CUtensorMap* store_map(const void* base, long long rows, int D) {
 template <int D, bool TMA>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, long long pool_pages,
                   const PagedKV& cache, const int* row_pos, const int* row_slot, void* out, float* partial,
-                  int R, int nq, int n_splits, int window, float scale, const float* sink, int cluster_merge,
-                  int* err, cudaStream_t s) {
+                  int R, int nq, int n_splits, int window, float scale, const float* sink,
+                  const float* slopes, int cluster_merge, int* err, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     const int n_htiles = (g + 7) / 8;
@@ -577,7 +585,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
                     cluster_merge ? n_splits : 1, *mk, *mv,
                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
                     cache, row_pos, row_slot, (__nv_bfloat16*)out, partial, nq, n_htiles, n_splits, window,
-                    scale * LOG2E, sink, cluster_merge, g_dtrace_next++, err);
+                    scale * LOG2E, sink, slopes, cluster_merge, g_dtrace_next++, err);
     if (e != cudaSuccess) return (int)e;
     if (n_splits > 1 && !cluster_merge)
         RFX_LAUNCH(attention_combine_kernel, R * nq, D <= 128 ? 64 : 128, 0, s, (const float*)partial,
@@ -588,8 +596,8 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
 int decode_entry(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                  int max_pages, int page_size, const int* row_pos, const int* row_slot, void* out,
                  float* partial, int R, int nq, int nkv, int head_dim, int n_splits, int window,
-                 float scale, const float* sink, int cluster_merge, long long pool_pages, int* err,
-                 void* stream) {
+                 float scale, const float* sink, const float* slopes, int cluster_merge,
+                 long long pool_pages, int* err, void* stream) {
     if (R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0 || n_splits < 1) return RFX_ERR_BAD_ARG;
     if (n_splits > 1 && !partial && !cluster_merge) return RFX_ERR_BAD_ARG;
@@ -609,7 +617,7 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
                      pool_pages * nkv * PAGE < 2147483647LL;
 #define RFX_GO(DD, T)                                                                                     \
     launch_decode<DD, T>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, R, nq, \
-                         n_splits, window, scale, sink, cluster_merge, err, s)
+                         n_splits, window, scale, sink, slopes, cluster_merge, err, s)
 #define RFX_CASE(DD)                                        \
     case DD:                                                \
         if (DD % 64 == 0 && tma) {                          \
@@ -636,16 +644,18 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
 // `pool_pages`: pages of the key (and value) store that `k_pages` points to, if the
 // caller knows (else 0): with it, head sizes 64, 128, 192 and 256 take their pages by
 // TMA.  `err` (may be null): a device word that receives a non-zero code if a bounded
-// wait ran out.
+// wait ran out.  `sink`, `slopes` (one float per query head each, or null): exp(sink)
+// joins the softmax's denominator; slope * (query position - key position) is taken
+// off every score.
 extern "C" int rfx_attention_decode(const void* q, const void* k_pages, const void* v_pages,
                                     const int* page_table, int max_pages, int page_size,
                                     const int* row_pos, const int* row_slot, void* out,
                                     float* partial, int R, int nq, int nkv, int head_dim,
                                     int n_splits, int window, float scale, const float* sink,
-                                    long long pool_pages, int* err, void* stream) {
+                                    const float* slopes, long long pool_pages, int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        partial, R, nq, nkv, head_dim, n_splits, window, scale, sink, 0, pool_pages, err,
-                        stream);
+                        partial, R, nq, nkv, head_dim, n_splits, window, scale, sink, slopes, 0, pool_pages,
+                        err, stream);
 }
 
 // The same with 2, 4, 8 or (where the device places such a cluster) 16 splits that
@@ -659,11 +669,11 @@ extern "C" int rfx_attention_decode_cluster(const void* q, const void* k_pages, 
                                             const int* page_table, int max_pages, int page_size,
                                             const int* row_pos, const int* row_slot, void* out, int R,
                                             int nq, int nkv, int head_dim, int n_splits, int window,
-                                            float scale, const float* sink, long long pool_pages,
-                                            int* err, void* stream) {
+                                            float scale, const float* sink, const float* slopes,
+                                            long long pool_pages, int* err, void* stream) {
     return decode_entry(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos, row_slot, out,
-                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, sink, 1, pool_pages, err,
-                        stream);
+                        nullptr, R, nq, nkv, head_dim, n_splits, window, scale, sink, slopes, 1, pool_pages,
+                        err, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -733,5 +743,5 @@ extern "C" int rfx_attention_decode_noalloc(const void* q, const void* k_pages, 
     // before the combine reads it, so nothing in the array has to start at zero
     return rfx_attention_decode(q, k_pages, v_pages, page_table, max_pages, page_size, row_pos,
                                 row_slot, out, scratch, R, nq, nkv, head_dim, n_splits, window, scale,
-                                nullptr, 0, nullptr, stream);
+                                nullptr, nullptr, 0, nullptr, stream);
 }

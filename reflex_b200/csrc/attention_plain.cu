@@ -8,7 +8,8 @@
 // For a query at position p of head h (kv head h / group): keys j in
 // [max(0, p - window + 1), p];  s_j = (q . K_j) * scale;  online softmax
 // m' = max(m, s), l = l e^(m-m') + e^(s-m'), acc = acc e^(m-m') + e^(s-m') V_j;
-// out = acc / l   (src/kernels_cuda/attention_online.cuh:64-102; the window
+// With `slopes` (one per query head) s_j loses slope * (p - j), a linear
+// distance bias.  out = acc / l   (src/kernels_cuda/attention_online.cuh:64-102; the window
 // rule is src/model/config.rs:1184-1185: i - j < window).
 //
 // Orders, which a host mirror repeats bit for bit: the dot product as a fused
@@ -32,7 +33,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
                        const T* __restrict__ v_pages, PagedKV cache,
                        const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                        T* __restrict__ out, int nq, int window, float scale,
-                       const float* __restrict__ sink) {
+                       const float* __restrict__ sink, const float* __restrict__ slopes) {
     pdl_prologue();
     const int d = cache.head_dim;
     const int r = blockIdx.x;
@@ -52,6 +53,7 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
         acc[i] = 0.0f;
     }
     float m = -INFINITY, l = 0.0f;
+    const float slope = slopes ? slopes[h] : 0.0f;
     for (int j = lo; j <= pos; ++j) {
         const size_t off = kv_offset(cache, slot, j, kvh);
         const T* kp = k_pages + off;
@@ -62,7 +64,9 @@ attention_plain_kernel(const T* __restrict__ q, const T* __restrict__ k_pages,
             const int e = i * 32 + lane;
             if (e < d) dot = fmaf(qv[i], ld<T>(kp, e), dot);
         }
-        const float s = warp_sum(dot) * scale;
+        float s = warp_sum(dot) * scale;
+        // a distance bias: slope * (query position - key position) off the score
+        if (slopes) s = fmaf(-slope, (float)(pos - j), s);
         const float m_new = fmaxf(m, s);
         const float corr = exact_expf(m - m_new);  // 0 at the first key (m = -inf)
         const float p = exact_expf(s - m_new);
@@ -98,7 +102,7 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
                                    const int* page_table, int max_pages, int page_size,
                                    const int* row_pos, const int* row_slot, void* out, int R,
                                    int nq, int nkv, int head_dim, int window, float scale,
-                                   const float* sink, void* stream) {
+                                   const float* sink, const float* slopes, void* stream) {
     if (R <= 0) return 0;
     if (head_dim <= 0 || head_dim > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
     if (nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
@@ -109,11 +113,11 @@ extern "C" int rfx_attention_plain(const void* q, const void* k_pages, const voi
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(attention_plain_kernel<float>, grid, 128, 0, s, (const float*)q,
                    (const float*)k_pages, (const float*)v_pages, cache, row_pos, row_slot,
-                   (float*)out, nq, window, scale, sink);
+                   (float*)out, nq, window, scale, sink, slopes);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(attention_plain_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)q,
                    (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, row_pos,
-                   row_slot, (__nv_bfloat16*)out, nq, window, scale, sink);
+                   row_slot, (__nv_bfloat16*)out, nq, window, scale, sink, slopes);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

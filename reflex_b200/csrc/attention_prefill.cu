@@ -30,7 +30,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
                          __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
-                         float scale_log2, const float* __restrict__ sink) {
+                         float scale_log2, const float* __restrict__ sink,
+                         const float* __restrict__ slopes) {
     constexpr int LD = D + 8;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [128][LD]
@@ -74,12 +75,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 
     // this thread's two rows: warp * 16 + lane / 4 and + 8
     int row_pos[2], row_lo[2];
+    float row_pen[2];  // the row's head's distance slope, times log2(e); 0 without slopes
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int row = warp * 16 + (lane >> 2) + 8 * h;
         const int p = pos_first + min(row / g, n_pos - 1);
         row_pos[h] = row < n_rows ? p : -1;  // rows beyond the tile see nothing
         row_lo[h] = (window > 0 && p + 1 > window) ? p + 1 - window : 0;
+        row_pen[h] = slopes ? slopes[kvh * g + row % g] * 1.4426950408889634f : 0.0f;
     }
     const int warp_row0 = warp * 16;
     const int warp_pos_max = pos_first + min((min(warp_row0 + 15, n_rows - 1)) / g, n_pos - 1);
@@ -116,8 +119,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                 const int j = base + key;
                 return j <= row_pos[h] && j >= row_lo[h];
             };
+            // a distance bias: slope * (query position - key position) off the score
+            auto penalty = [&](int key, int h) { return row_pen[h] * (float)(row_pos[h] - (base + key)); };
             attend_tile<D, 8>(qs + warp_row0 * LD, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, 0,
-                              scale_log2, visible, m, l, acc);
+                              scale_log2, visible, penalty, m, l, acc);
         }
         __syncthreads();
     }
@@ -142,7 +147,7 @@ template <int D>
 int launch_prefill(const void* q, const void* k_pages, const void* v_pages, const PagedKV& cache,
                    const int* seq_slot, const int* seq_start, const int* seq_new,
                    const int* seq_row0, void* out, int S, int max_new, int nq, int window,
-                   float scale, const float* sink, cudaStream_t s) {
+                   float scale, const float* sink, const float* slopes, cudaStream_t s) {
     constexpr int LD = D + 8;
     const int g = nq / cache.n_kv_heads;
     if (g > PF_ROWS) return RFX_ERR_UNSUPPORTED;
@@ -155,7 +160,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, PF_THREADS, smem, s, (const __nv_bfloat16*)q,
                (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, cache, seq_slot, seq_start,
-               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink);
+               seq_new, seq_row0, (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, slopes);
     return 0;
 }
 
@@ -164,13 +169,16 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, cons
 // bfloat16 q and out [rows, nq, D] packed by sequence; seq_* describe the S
 // sequences of the step (slot, positions already cached, rows in this step,
 // first row).  The cache must already hold this step's keys and values.
+// `sink` and `slopes` (one float per query head each, or null): exp(sink) joins
+// the softmax's denominator; slope * (query position - key position) is taken
+// off every score.
 // head_dim: multiples of 16 up to 256; group size nq / nkv up to 128; page 64.
 extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const void* v_pages,
                                      const int* page_table, int max_pages, int page_size,
                                      const int* seq_slot, const int* seq_start, const int* seq_new,
                                      const int* seq_row0, void* out, int S, int max_new, int nq,
                                      int nkv, int head_dim, int window, float scale, const float* sink,
-                                     void* stream) {
+                                     const float* slopes, void* stream) {
     if (S <= 0 || max_new <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
@@ -178,7 +186,7 @@ extern "C" int rfx_attention_prefill(const void* q, const void* k_pages, const v
 #define RFX_CASE(DD)                                                                              \
     case DD:                                                                                      \
         return launch_prefill<DD>(q, k_pages, v_pages, cache, seq_slot, seq_start, seq_new,       \
-                                  seq_row0, out, S, max_new, nq, window, scale, sink, s);
+                                  seq_row0, out, S, max_new, nq, window, scale, sink, slopes, s);
     switch (head_dim) {
         RFX_CASE(16) RFX_CASE(32) RFX_CASE(48) RFX_CASE(64) RFX_CASE(80) RFX_CASE(96)
         RFX_CASE(112) RFX_CASE(128) RFX_CASE(144) RFX_CASE(160) RFX_CASE(176) RFX_CASE(192)

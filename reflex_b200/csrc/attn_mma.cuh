@@ -86,10 +86,12 @@ __device__ __forceinline__ void load_tile_async(__nv_bfloat16* smem, const __nv_
 //   kvalid(j): whether tile key j (0-based in the tile) is visible to row half
 //   hrow (0: row lane/4, 1: row lane/4 + 8)
 // scale_log2 = scale * log2(e); probabilities are 2^(s * scale_log2 - m).
-template <int D, int NT, typename Visible>
+//   penalty(j, hrow): what is taken off a visible key's scaled score (a distance
+//   bias, already times log2(e)); 0.0f leaves the score's bits as they are
+template <int D, int NT, typename Visible, typename Penalty>
 __device__ __forceinline__ void attend_tile(const __nv_bfloat16* qs, const __nv_bfloat16* ks,
                                             const __nv_bfloat16* vs, int key0, float scale_log2,
-                                            Visible visible, float (&m)[2], float (&l)[2],
+                                            Visible visible, Penalty penalty, float (&m)[2], float (&l)[2],
                                             float (&acc)[D / 8][4]) {
     static_assert(NT % 2 == 0, "keys come in pairs of 8-key tiles");
     const int lane = threadIdx.x & 31;
@@ -122,7 +124,7 @@ __device__ __forceinline__ void attend_tile(const __nv_bfloat16* qs, const __nv_
         for (int i = 0; i < 4; ++i) {
             const int key = key0 + t * 8 + 2 * (lane & 3) + (i & 1);
             const int h = i >> 1;
-            const float v = visible(key, h) ? s[t][i] * scale_log2 : -INFINITY;
+            const float v = visible(key, h) ? s[t][i] * scale_log2 - penalty(key, h) : -INFINITY;
             s[t][i] = v;
             mx[h] = fmaxf(mx[h], v);
         }
@@ -214,11 +216,15 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
     return tile + row * (D + 8) + col;
 }
 
+//   pen[2], dist0: a distance bias on the scores.  Tile key j lies dist0 - j
+//   positions before the query, and pen[i] * (dist0 - j) is taken off its scaled
+//   score for the thread's i-th head (slope times log2(e); 0.0f: no bias, the
+//   score's bits stay as they are)
 template <int D, bool SWZ = false, typename Visible>
 __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], const __nv_bfloat16* ks,
                                               const __nv_bfloat16* vs, int key0, float scale_log2,
-                                              Visible visible, float (&m)[2], float (&l)[2],
-                                              float (&acc)[D / 16][4]) {
+                                              Visible visible, const float (&pen)[2], int dist0,
+                                              float (&m)[2], float (&l)[2], float (&acc)[D / 16][4]) {
     const int lane = threadIdx.x & 31;
     float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
@@ -231,10 +237,11 @@ __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], c
     const int ka = key0 + (lane >> 2), kb = ka + 8;
     const bool va = visible(ka), vb = visible(kb);
     float v[4];
-    v[0] = va ? s[0] * scale_log2 : -INFINITY;
-    v[1] = va ? s[1] * scale_log2 : -INFINITY;
-    v[2] = vb ? s[2] * scale_log2 : -INFINITY;
-    v[3] = vb ? s[3] * scale_log2 : -INFINITY;
+    const float da = (float)(dist0 - ka), db = (float)(dist0 - kb);
+    v[0] = va ? s[0] * scale_log2 - pen[0] * da : -INFINITY;
+    v[1] = va ? s[1] * scale_log2 - pen[1] * da : -INFINITY;
+    v[2] = vb ? s[2] * scale_log2 - pen[0] * db : -INFINITY;
+    v[3] = vb ? s[3] * scale_log2 - pen[1] * db : -INFINITY;
     float corr[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {

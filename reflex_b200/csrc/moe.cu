@@ -1,14 +1,18 @@
 // Mixture-of-experts feed-forward with top-k routing, for any number of rows.
 //
 //  * rfx_moe_route: router logits (32-bit, bias added here) -> the `top`
-//    experts with the largest logits (ties: the lower index) and their weights,
-//    the softmax over the chosen logits only.  One warp a row.
-//  * rfx_moe_up: act[(r, k), :] = f(W_up[e] x[r]) for expert e = ids[r, k];
-//    f = relu squared (act 0) or silu (act 1).  One warp an output element,
-//    the row in shared memory.
+//    experts with the largest logits (ties: the lower index) and their weights:
+//    the softmax over the chosen logits only (mode 0), or each chosen logit's
+//    sigmoid, not renormalised (mode 1).  One warp a row.
+//  * rfx_moe_up: act[(r, k), :] = f(W_up[e] (s x[r])) for expert e = ids[r, k];
+//    f = relu squared (act 0) or silu (act 1); act 2 is the gated, clamped form
+//    over W_up[e] = [gate rows | up rows]: g' = min(g, limit), u' = clamp(u,
+//    -limit, limit), g' sigmoid(alpha g') (u' + 1).  `in_scale` (may be null)
+//    gives s per (row, choice): a weight on the expert's input.  One warp an
+//    output element, the row in shared memory.
 //  * rfx_moe_down: y[r, :] = sum_k wts[r, k] W_down[ids[r, k]] act[(r, k), :],
 //    the experts in the order of their rank, 32-bit sums: a row's result does
-//    not depend on the batch.
+//    not depend on the batch.  Null `wts`: every weight is one.
 //  * Many rows (prefill): rfx_moe_group places the (row, choice) pairs expert by
 //    expert (counts, offsets, each pair's place), rfx_moe_gather copies the
 //    rows into that order, the library multiplies each expert's block by its
@@ -23,8 +27,9 @@ using namespace rfx;
 
 constexpr int MAX_PER_LANE = 8;  // up to 256 experts
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
-                                 int* __restrict__ ids, float* __restrict__ wts, int R, int E, int top) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, int ld, const float* __restrict__ bias,
+                                 int* __restrict__ ids, float* __restrict__ wts, int R, int E, int top,
+                                 int mode) {
     pdl_prologue();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -33,9 +38,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
         const int e = i * 32 + lane;
-        z[i] = e < E ? logits[(size_t)r * E + e] + (bias ? bias[e] : 0.0f) : -INFINITY;
+        z[i] = e < E ? logits[(size_t)r * ld + e] + (bias ? bias[e] : 0.0f) : -INFINITY;
     }
-    float zmax = 0.0f, sum = 0.0f, mine = 0.0f;  // lane k keeps the k-th choice's exponential
+    float zmax = 0.0f, sum = mode == 1 ? 1.0f : 0.0f, mine = 0.0f;  // lane k keeps the k-th choice's exponential
     int my_id = 0;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -52,8 +57,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, const float* 
             if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
         }
         if (k == 0) zmax = best;
-        const float p = expf(best - zmax);
-        sum += p;
+        // mode 1: the chosen logit's sigmoid is the weight as it is (sum stays one)
+        const float p = mode == 1 ? 1.0f / (1.0f + expf(-best)) : expf(best - zmax);
+        if (mode != 1) sum += p;
         if ((k & 31) == lane && k < 32) { mine = p; my_id = best_e; }
         if (k >= 32 && lane == 0) {  // more than 32 choices: written unnormalised, scaled below
             ids[(size_t)r * top + k] = best_e;
@@ -115,20 +121,36 @@ __device__ __forceinline__ float warp_dot(const float* __restrict__ xs, const T*
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_up_kernel(const T* __restrict__ x, const T* __restrict__ W, const int* __restrict__ ids,
-              T* __restrict__ act, int top, int ff, int width, int kind) {
+              const float* __restrict__ in_scale, T* __restrict__ act, int top, int ff, int width, int kind,
+              float alpha, float limit) {
     extern __shared__ __align__(16) float xs[];  // the row
     pdl_prologue();
     const int pair = blockIdx.x;
     const int r = pair / top;
     const int e = ids[pair];
-    for (int c = threadIdx.x; c < width; c += blockDim.x) xs[c] = ld<T>(x, (size_t)r * width + c);
+    // a weight on the expert's input; the scaled row is rounded to the storage type,
+    // as the rows of the grouped form are
+    const float sc = in_scale ? in_scale[pair] : 1.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = ld<T>(x, (size_t)r * width + c);
+        if (in_scale) {
+            if constexpr (sizeof(T) == 2) xs[c] = __bfloat162float(__float2bfloat16_rn(v * sc));
+            else xs[c] = v * sc;
+        } else xs[c] = v;
+    }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    const T* We = W + (size_t)e * ff * width;
+    const T* We = W + (size_t)e * (kind == 2 ? 2 : 1) * ff * width;
     for (int j = blockIdx.y * nwarps + warp; j < ff; j += gridDim.y * nwarps) {
         const T* wrow = We + (size_t)j * width;
         const float dot = warp_dot<T>(xs, wrow, width, lane);
-        if (lane == 0) {
+        if (kind == 2) {
+            const float up = warp_dot<T>(xs, wrow + (size_t)ff * width, width, lane);
+            if (lane == 0) {
+                const float g = fminf(dot, limit), u = fminf(fmaxf(up, -limit), limit);
+                st<T>(act, (size_t)pair * ff + j, (g / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+            }
+        } else if (lane == 0) {
             float a;
             if (kind == 0) { a = fmaxf(dot, 0.0f); a *= a; }
             else a = dot / (1.0f + expf(-dot));
@@ -151,7 +173,7 @@ moe_down_kernel(const T* __restrict__ act, const T* __restrict__ W, const int* _
         float total = 0.0f;
         for (int k = 0; k < top; ++k) {
             const T* wrow = W + ((size_t)ids[(size_t)r * top + k] * width + n) * ff;
-            total = fmaf(wts[(size_t)r * top + k], warp_dot<T>(as + k * ff, wrow, ff, lane), total);
+            total = fmaf(wts ? wts[(size_t)r * top + k] : 1.0f, warp_dot<T>(as + k * ff, wrow, ff, lane), total);
         }
         if (lane == 0) y[(size_t)r * width + n] = total;
     }
@@ -183,16 +205,19 @@ moe_group_kernel(const int* __restrict__ ids, int n_pairs, int E, int* __restric
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) place[p] = atomicAdd(&cursor[ids[p]], 1);
 }
 
-// xg[place[p], :] = x[p / top, :]
+// xg[place[p], :] = x[p / top, :] (times scale[p], when given)
 template <typename T>
 __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict__ place,
-                                  T* __restrict__ xg, int top, int width) {
+                                  const float* __restrict__ scale, T* __restrict__ xg, int top, int width) {
     pdl_prologue();
     const int p = blockIdx.x;
     const T* src = x + (size_t)(p / top) * width;
     T* dst = xg + (size_t)place[p] * width;
     const int bytes = width * (int)sizeof(T);
-    if ((bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+    if (scale) {
+        const float sc = scale[p];
+        for (int c = threadIdx.x; c < width; c += blockDim.x) st<T>(dst, c, ld<T>(src, c) * sc);
+    } else if ((bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
         for (int c = threadIdx.x; c < bytes / 16; c += blockDim.x)
             reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
     } else {
@@ -221,7 +246,8 @@ __global__ void moe_combine_kernel(const T* __restrict__ yg, const int* __restri
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float total = 0.0f;
         for (int k = 0; k < top; ++k)
-            total = fmaf(wts[(size_t)r * top + k], ld<T>(yg, (size_t)place[(size_t)r * top + k] * width + c), total);
+            total = fmaf(wts ? wts[(size_t)r * top + k] : 1.0f,
+                         ld<T>(yg, (size_t)place[(size_t)r * top + k] * width + c), total);
         y[(size_t)r * width + c] = total;
     }
 }
@@ -236,14 +262,15 @@ extern "C" int rfx_moe_group(const int* ids, int n_pairs, int E, int* offsets, i
     return 0;
 }
 
-extern "C" int rfx_moe_gather(const void* x, const int* place, void* xg, int dt, int n_pairs, int top,
-                              int width, void* stream) {
+extern "C" int rfx_moe_gather(const void* x, const int* place, const float* scale, void* xg, int dt,
+                              int n_pairs, int top, int width, void* stream) {
     if (n_pairs <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(moe_gather_kernel<float>, n_pairs, 128, 0, s, (const float*)x, place, (float*)xg, top, width);
+        RFX_LAUNCH(moe_gather_kernel<float>, n_pairs, 128, 0, s, (const float*)x, place, scale, (float*)xg, top,
+                   width);
     else if (dt == RFX_DT_BF16)
-        RFX_LAUNCH(moe_gather_kernel<__nv_bfloat16>, n_pairs, 128, 0, s, (const __nv_bfloat16*)x, place,
+        RFX_LAUNCH(moe_gather_kernel<__nv_bfloat16>, n_pairs, 128, 0, s, (const __nv_bfloat16*)x, place, scale,
                    (__nv_bfloat16*)xg, top, width);
     else
         return RFX_ERR_BAD_ARG;
@@ -278,17 +305,19 @@ extern "C" int rfx_moe_combine(const void* yg, int dt, const int* place, const f
     return 0;
 }
 
-extern "C" int rfx_moe_route(const float* logits, const float* bias, int* ids, float* wts, int R, int E,
-                             int top, void* stream) {
+// `ld`: floats between two rows of `logits` (>= E: further columns are ignored)
+extern "C" int rfx_moe_route(const float* logits, int ld, const float* bias, int* ids, float* wts, int R, int E,
+                             int top, int mode, void* stream) {
     if (R <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E) return RFX_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || top > E || ld < E || (mode != 0 && mode != 1)) return RFX_ERR_BAD_ARG;
     if (E > 32 * MAX_PER_LANE) return RFX_ERR_UNSUPPORTED;
-    RFX_LAUNCH(moe_route_kernel, (R + 3) / 4, 128, 0, (cudaStream_t)stream, logits, bias, ids, wts, R, E, top);
+    RFX_LAUNCH(moe_route_kernel, (R + 3) / 4, 128, 0, (cudaStream_t)stream, logits, ld, bias, ids, wts, R, E, top,
+               mode);
     return 0;
 }
 
-extern "C" int rfx_moe_up(const void* x, const void* W, const int* ids, void* act, int dt, int R, int top,
-                          int ff, int width, int kind, void* stream) {
+extern "C" int rfx_moe_up(const void* x, const void* W, const int* ids, const float* in_scale, void* act, int dt,
+                          int R, int top, int ff, int width, int kind, float alpha, float limit, void* stream) {
     if (R <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return RFX_ERR_UNSUPPORTED;
@@ -303,8 +332,8 @@ extern "C" int rfx_moe_up(const void* x, const void* W, const int* ids, void* ac
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                         \
         }                                                                                                \
-        RFX_LAUNCH(moe_up_kernel<T>, grid, 256, smem, s, (const T*)x, (const T*)W, ids, (T*)act, top, ff,  \
-                   width, kind);                                                                         \
+        RFX_LAUNCH(moe_up_kernel<T>, grid, 256, smem, s, (const T*)x, (const T*)W, ids, in_scale, (T*)act, \
+                   top, ff, width, kind, alpha, limit);                                                  \
     } while (0)
     if (dt == RFX_DT_F32) RFX_GO(float);
     else if (dt == RFX_DT_BF16) RFX_GO(__nv_bfloat16);

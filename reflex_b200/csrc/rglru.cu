@@ -1,0 +1,88 @@
+// A real-gated linear recurrence, channel by channel, across steps.
+//
+// With u the recurrence's input (a short convolution's output), r_pre and
+// i_pre the two gates' pre-activations (block-diagonal products of u, made
+// before this kernel; their biases are added here), lam a learned number a
+// channel and y_pre the other branch's projection:
+//   r = sigmoid(r_pre + rb),  i = sigmoid(i_pre + ib)
+//   log a = -c * r * softplus(lam),  a = exp(log a)
+//   S_t = a S_(t-1) + sqrt(1 - a^2) * (i * u)          S = 0 before the first token
+//   out_t = S_t * gelu_tanh(y_pre + yb)
+// All of it is 32-bit; sqrt(1 - a^2) is taken as sqrt(-expm1(2 log a)), which
+// keeps its digits when a is close to one.  S lives in the cache's state
+// ([slot][...], at `state_off`), read when a step begins and stored when it
+// ends.  A thread owns one channel of one sequence and walks the step's rows
+// in order.
+#include "common.cuh"
+
+namespace {
+
+using namespace rfx;
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// gates: [R][blocks][2 * K] (a block's r_pre, then its i_pre); channel c = b * K + k
+template <typename TO>
+__global__ void __launch_bounds__(128)
+rglru_scan_kernel(const float* __restrict__ u, const float* __restrict__ gates,
+                  const float* __restrict__ r_bias, const float* __restrict__ i_bias,
+                  const float* __restrict__ lam, float decay_scale, const float* __restrict__ proj, int ld,
+                  int y_off, const float* __restrict__ y_bias, float* __restrict__ state, size_t slot_stride,
+                  size_t state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                  TO* __restrict__ out, int W, int K) {
+    pdl_prologue();
+    const int s = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= W) return;
+    const int row0 = seq_row0[s], n = seq_row0[s + 1] - row0;
+    float* sp = state + (size_t)seq_slot[s] * slot_stride + state_off + c;
+    const int b = c / K, k = c % K;
+    const size_t g_r = (size_t)b * 2 * K + k, g_i = g_r + K;
+    const float rb = r_bias ? r_bias[c] : 0.0f, ib = i_bias ? i_bias[c] : 0.0f;
+    const float yb = y_bias ? y_bias[c] : 0.0f;
+    const float rate = -decay_scale * softplus_f(lam[c]);
+    float S = *sp;
+#pragma unroll 4
+    for (int t = 0; t < n; ++t) {
+        const size_t row = (size_t)(row0 + t);
+        const float uv = u[row * W + c];
+        const float r = sigmoid_f(gates[row * 2 * W + g_r] + rb);
+        const float i = sigmoid_f(gates[row * 2 * W + g_i] + ib);
+        const float yv = gelu_tanh_f(proj[row * ld + y_off + c] + yb);
+        const float log_a = rate * r;
+        const float a = expf(log_a);
+        const float step = sqrtf(-expm1f(2.0f * log_a));
+        S = fmaf(a, S, step * (i * uv));
+        st<TO>(out, row * W + c, S * yv);
+    }
+    *sp = S;
+}
+
+}  // namespace
+
+extern "C" int rfx_rglru_scan(const float* u, const float* gates, const float* r_bias, const float* i_bias,
+                              const float* lam, float decay_scale, const float* proj, int ld, int y_off,
+                              const float* y_bias, float* state, long long slot_stride, long long state_off,
+                              const int* seq_slot, const int* seq_row0, int S, void* out, int out_dt, int W,
+                              int blocks, void* stream) {
+    if (S <= 0 || W <= 0) return 0;
+    if (blocks <= 0 || W % blocks != 0) return RFX_ERR_BAD_ARG;
+    dim3 grid(S, (W + 127) / 128);
+    cudaStream_t s = (cudaStream_t)stream;
+    const int K = W / blocks;
+    if (out_dt == RFX_DT_F32)
+        RFX_LAUNCH(rglru_scan_kernel<float>, grid, 128, 0, s, u, gates, r_bias, i_bias, lam, decay_scale, proj,
+                   ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off, seq_slot, seq_row0,
+                   (float*)out, W, K);
+    else if (out_dt == RFX_DT_BF16)
+        RFX_LAUNCH(rglru_scan_kernel<__nv_bfloat16>, grid, 128, 0, s, u, gates, r_bias, i_bias, lam,
+                   decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off,
+                   seq_slot, seq_row0, (__nv_bfloat16*)out, W, K);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}

@@ -1,0 +1,164 @@
+// Small row-wise ops around the residual stream, all with 32-bit arithmetic.
+//
+//  * rfx_branch_norm_mean: two branches' outputs, each over its root mean
+//    square times its own weight, averaged:
+//        out = ((a + a_bias) / rms(a + a_bias) * wa + b / rms(b) * wb) / 2
+//  * rfx_glu_clamped: the clamped gated activation
+//        g' = min(g, limit), u' = clamp(u, -limit, limit),
+//        out = g' * sigmoid(alpha * g') * (u' + 1)
+//    of a row [gates | ups] (or gate_j at 2j and up_j at 2j + 1).
+//  * rfx_row_gate_add: y[r] += sigmoid(z[r]) * s[r], one gate a row.
+//  * rfx_stream_concat: out[r] = [x[r] (+ delta[r]) | x0[r]], cast, the input of
+//    a product that mixes the stream with the embedding output.
+//  * rfx_logit_finish: z <- z * scale, then cap * tanh(z / cap) when cap > 0.
+#include "common.cuh"
+
+namespace {
+
+using namespace rfx;
+
+__global__ void __launch_bounds__(256)
+branch_norm_mean_kernel(const float* __restrict__ a, const float* __restrict__ a_bias,
+                        const float* __restrict__ wa, const float* __restrict__ b,
+                        const float* __restrict__ wb, float eps, float* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    float sa = 0.0f, sb = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = a[r * H + c] + (a_bias ? a_bias[c] : 0.0f);
+        const float y = b[r * H + c];
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    const float ra = rsqrtf(block_sum(sa, scratch) / (float)H + eps);
+    const float rb = rsqrtf(block_sum(sb, scratch) / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float x = a[r * H + c] + (a_bias ? a_bias[c] : 0.0f);
+        const float y = b[r * H + c];
+        out[r * H + c] = 0.5f * fmaf(x * ra, wa[c], (y * rb) * wb[c]);
+    }
+}
+
+__device__ __forceinline__ float glu_clamped(float g, float u, float alpha, float limit) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+template <typename T>
+__global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int R, int I, int alternating,
+                                   float alpha, float limit) {
+    pdl_prologue();
+    const size_t n = (size_t)R * I;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / I, c = i % I;
+        const float g = ld<T>(gu, r * 2 * I + (alternating ? 2 * c : c));
+        const float u = ld<T>(gu, r * 2 * I + (alternating ? 2 * c + 1 : I + c));
+        st<T>(out, i, glu_clamped(g, u, alpha, limit));
+    }
+}
+
+template <typename T>
+__global__ void row_gate_add_kernel(float* __restrict__ y, const T* __restrict__ s, const float* __restrict__ z,
+                                    int ldz, int col, int H) {
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    const float gate = 1.0f / (1.0f + expf(-z[r * ldz + col]));
+    for (int c = threadIdx.x; c < H; c += blockDim.x) y[r * H + c] = fmaf(gate, ld<T>(s, r * H + c), y[r * H + c]);
+}
+
+template <typename TD, typename TO>
+__global__ void stream_concat_kernel(const float* __restrict__ x, const TD* __restrict__ delta,
+                                     const float* __restrict__ x0, TO* __restrict__ out, int H) {
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = x[r * H + c];
+        if (delta) v += ld<TD>(delta, r * H + c);
+        st<TO>(out, r * 2 * H + c, v);
+        st<TO>(out, r * 2 * H + H + c, x0[r * H + c]);
+    }
+}
+
+__global__ void logit_finish_kernel(float* __restrict__ z, size_t n, float scale, float cap) {
+    pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float v = z[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v / cap);
+        z[i] = v;
+    }
+}
+
+int blocks_for(size_t n) {
+    size_t b = (n + 255) / 256;
+    const size_t most = (size_t)sm_count() * 16;
+    return (int)(b > most ? most : (b < 1 ? 1 : b));
+}
+
+}  // namespace
+
+extern "C" int rfx_branch_norm_mean(const float* a, const float* a_bias, const float* wa, const float* b,
+                                    const float* wb, float eps, float* out, int R, int H, void* stream) {
+    if (R <= 0 || H <= 0) return 0;
+    RFX_LAUNCH(branch_norm_mean_kernel, R, H >= 1024 ? 256 : 128, 0, (cudaStream_t)stream, a, a_bias, wa, b, wb,
+               eps, out, H);
+    return 0;
+}
+
+extern "C" int rfx_glu_clamped(const void* gate_up, void* out, int dt, int R, int I, int alternating,
+                               float alpha, float limit, void* stream) {
+    if (R <= 0 || I <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int blocks = blocks_for((size_t)R * I);
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(glu_clamped_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I,
+                   alternating, alpha, limit);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(glu_clamped_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
+                   (__nv_bfloat16*)out, R, I, alternating, alpha, limit);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
+
+extern "C" int rfx_row_gate_add(float* y, const void* s_rows, int dt, const float* z, int ldz, int col, int R,
+                                int H, void* stream) {
+    if (R <= 0 || H <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == RFX_DT_F32)
+        RFX_LAUNCH(row_gate_add_kernel<float>, R, 256, 0, s, y, (const float*)s_rows, z, ldz, col, H);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(row_gate_add_kernel<__nv_bfloat16>, R, 256, 0, s, y, (const __nv_bfloat16*)s_rows, z, ldz,
+                   col, H);
+    else
+        return RFX_ERR_BAD_ARG;
+    return 0;
+}
+
+extern "C" int rfx_stream_concat(const float* x, const void* delta, int delta_dt, const float* x0, void* out,
+                                 int out_dt, int R, int H, void* stream) {
+    if (R <= 0 || H <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool dbf = delta && delta_dt == RFX_DT_BF16;
+    if (delta && delta_dt != RFX_DT_BF16 && delta_dt != RFX_DT_F32) return RFX_ERR_BAD_ARG;
+#define RFX_GO(TD, TO)                                                                                   \
+    RFX_LAUNCH((stream_concat_kernel<TD, TO>), R, 256, 0, s, x, (const TD*)delta, x0, (TO*)out, H)
+    if (out_dt == RFX_DT_F32) {
+        if (dbf) RFX_GO(__nv_bfloat16, float);
+        else RFX_GO(float, float);
+    } else if (out_dt == RFX_DT_BF16) {
+        if (dbf) RFX_GO(__nv_bfloat16, __nv_bfloat16);
+        else RFX_GO(float, __nv_bfloat16);
+    } else
+        return RFX_ERR_BAD_ARG;
+#undef RFX_GO
+    return 0;
+}
+
+extern "C" int rfx_logit_finish(float* z, long long n, float scale, float cap, void* stream) {
+    if (n <= 0) return 0;
+    RFX_LAUNCH(logit_finish_kernel, blocks_for((size_t)n), 256, 0, (cudaStream_t)stream, z, (size_t)n, scale,
+               cap);
+    return 0;
+}

@@ -29,6 +29,9 @@ class RunContext:
     kv: Any = None             # KVView of this run's cache entry, if it has one
     state: Any = None          # [slots, *shape] tensor of this run's state, if any
     entry: int = -1
+    # a mixer whose `cache_spec()` is a tuple: its views, in the tuple's order
+    # (`kv` and `state` are then the first of each kind)
+    parts: Any = None
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[str, ...], TensorInfo]]:
@@ -42,6 +45,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[str, ...], Tensor
     for li, layer in enumerate(spec.layers):
         for name, (part, role, info) in BLOCKS.get(layer.block).tensor_names(layer).items():
             out[name] = (("layer", str(li), part, role), info)
+    if spec.stream_mix_name is not None:
+        out[spec.stream_mix_name] = (("stream_mix",), TensorInfo((spec.hidden_size, 2 * spec.hidden_size), "matrix"))
     out[spec.final_norm_name] = (("final_norm",), TensorInfo((spec.final_norm.size,), "norm"))
     if not spec.tie_word_embeddings:
         out[spec.head_name] = (("head",), TensorInfo((spec.vocab_size, spec.hidden_size), "matrix"))
@@ -60,6 +65,9 @@ class CausalLM:
         self.embedding_terms = [EMBEDDING_TERMS.get(t.kind)(t, dtype, self.device) for t in spec.embedding_terms]
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self.stream_mix: Optional[torch.Tensor] = None
+        if any(r.mixes_input for r in spec.run_order) and spec.stream_mix_name is None:
+            raise ValueError("a run mixes its input but the model names no stream-mix matrix")
 
     @property
     def capturable(self) -> bool:
@@ -88,6 +96,8 @@ class CausalLM:
                 self.head = t.to(device=self.device, dtype=self.dtype).contiguous()
             elif where[0] == "final_norm":
                 self.final_norm.bind({"weight": t})
+            elif where[0] == "stream_mix":
+                self.stream_mix = t.to(device=self.device, dtype=self.dtype).contiguous()
             elif where[0] == "embedding_term":
                 per_term.setdefault(int(where[1]), {})[where[2]] = t
             else:
@@ -131,17 +141,36 @@ class CausalLM:
         ops.prof_mark("embed")
         pending = None
         order = self.spec.run_order
+        # the embedding output, for the runs that start from a mix of it and the stream
+        x0 = ops.keep_copy(h) if any(r.mixes_input for r in order) else None
         for i, run in enumerate(order):
             # the norm that will consume this run's result: the next run's first norm, or the final one
-            next_norm = (getattr(self.layers[order[i + 1].layer], "fusable_first_norm", None)
-                         if i + 1 < len(order) else self.final_norm)
+            if i + 1 == len(order):
+                next_norm = self.final_norm
+            elif order[i + 1].mixes_input:
+                next_norm = None  # the stream goes through the mix first: no norm to begin here
+            else:
+                next_norm = getattr(self.layers[order[i + 1].layer], "fusable_first_norm", None)
             ops.workspace.next_phase()  # this run's working memory; the last run's results stay readable
+            if run.mixes_input:
+                # x <- W [x; x0]: the stream (with what the run before left to add) beside the
+                # embedding output, through one product; the new stream is 32-bit
+                if isinstance(pending, ops.NormedInput):
+                    pending = None  # the stream already holds the sum
+                both = ops.stream_concat(h, pending, x0, self.dtype)
+                h.copy_(ops.linear(both, self.stream_mix, out_dtype=torch.float32))  # the stream's own memory
+                pending = None
+                ops.prof_mark("stream_mix")
             ctx = RunContext(batch=batch, writes_cache=run.writes_cache, entry=run.cache)
             kind = cache.has(run.cache)
             if kind == "kv":
                 ctx.kv = cache.kv(run.cache)
             elif kind == "state":
                 ctx.state = cache.state(run.cache)
+            elif kind == "parts":
+                ctx.parts = cache.views(run.cache)
+                ctx.kv = next((v for v in ctx.parts if not isinstance(v, torch.Tensor)), None)
+                ctx.state = next((v for v in ctx.parts if isinstance(v, torch.Tensor)), None)
             layer = self.layers[run.layer]
             if hasattr(layer, "fusable_first_norm"):
                 h, pending = layer.forward(h, pending, ctx, next_norm=next_norm)
@@ -160,9 +189,16 @@ class CausalLM:
         else:
             normed = self.final_norm(hidden, delta=pending, rows=rows)
         out = ops.linear(normed, self.head, out_dtype=torch.float32, own=True)  # the caller's to keep
+        out = self.finish_logits(out)
+        ops.prof_mark("head")
+        return out
+
+    def finish_logits(self, out: torch.Tensor) -> torch.Tensor:
+        """The model's scale on the logits and, where it has one, the tanh cap."""
+        if self.spec.logit_softcap:
+            return ops.logit_finish_(out, self.spec.logit_scale, self.spec.logit_softcap)
         if self.spec.logit_scale != 1.0:
             out = out * self.spec.logit_scale
-        ops.prof_mark("head")
         return out
 
     def normed_rows(self, hidden: torch.Tensor, pending, rows: torch.Tensor) -> torch.Tensor:
@@ -176,9 +212,7 @@ class CausalLM:
         (`ids`, int32 on the device, one per wanted row), float32 [wanted]: only
         those rows of the head are read (src/model/dense.rs:2073-2133)."""
         h, pending = self.hidden_states(batch, cache)
-        out = ops.gather_dot(self.normed_rows(h, pending, batch.want_rows), self.head, ids)
-        if self.spec.logit_scale != 1.0:
-            out = out * self.spec.logit_scale
+        out = self.finish_logits(ops.gather_dot(self.normed_rows(h, pending, batch.want_rows), self.head, ids))
         ops.prof_mark("head")
         return out
 

@@ -472,9 +472,12 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
                     page_table: torch.Tensor, page_size: int, row_pos: torch.Tensor,
                     row_slot: torch.Tensor, nq: int, nkv: int, head_dim: int,
                     window: Optional[int], scale: float,
-                    sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sink: Optional[torch.Tensor] = None,
+                    slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`sink` (float32, one per query head): exp(sink) joins the softmax's
-    denominator once, with no key and no value."""
+    denominator once, with no key and no value.  `slopes` (float32, one per
+    query head): slope * (query position - key position) is taken off every
+    score, a linear distance bias."""
     R = q.shape[0]
     out = _new(q.shape, q.dtype, q.device)
     st = native.lib().rfx_attention_plain(
@@ -482,7 +485,7 @@ def attention_plain(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tenso
         dt_code(q.dtype), _chk(page_table, "page_table", torch.int32), page_table.shape[1],
         page_size, _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32),
         out.data_ptr(), R, nq, nkv, head_dim, int(window or 0), float(scale),
-        _chk(sink, "sink", torch.float32), _stream())
+        _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32), _stream())
     native.check(st, f"attention_plain (head_dim={head_dim})")
     return out
 
@@ -552,7 +555,8 @@ def decode_splits(n_rows: int, nq: int, nkv: int, max_pages: int = 64) -> int:
 
 def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_slot, nq, nkv,
                      head_dim, window, scale, n_splits: Optional[int] = None,
-                     sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     sink: Optional[torch.Tensor] = None,
+                     slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 tensor-core attention for rows that are each one query
     position (decode), split over the keys."""
     R = q.shape[0]
@@ -571,7 +575,7 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
             _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
             _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
             R, nq, nkv, head_dim, n_splits, int(window or 0), float(scale), _chk(sink, "sink", torch.float32),
-            pool_pages, device_error_word(q.device).data_ptr(), _stream())
+            _chk(slopes, "slopes", torch.float32), pool_pages, device_error_word(q.device).data_ptr(), _stream())
         if st != native.ERR_UNSUPPORTED:
             native.check(st, f"attention_decode_cluster (head_dim={head_dim}, splits={n_splits})")
             return out
@@ -581,8 +585,8 @@ def attention_decode(q, k_pages, v_pages, page_table, page_size, row_pos, row_sl
         _chk(page_table, "page_table", torch.int32), page_table.shape[1], page_size,
         _chk(row_pos, "row_pos", torch.int32), _chk(row_slot, "row_slot", torch.int32), out.data_ptr(),
         partial.data_ptr() if partial is not None else 0, R, nq, nkv, head_dim, n_splits,
-        int(window or 0), float(scale), _chk(sink, "sink", torch.float32), pool_pages,
-        device_error_word(q.device).data_ptr(), _stream())
+        int(window or 0), float(scale), _chk(sink, "sink", torch.float32),
+        _chk(slopes, "slopes", torch.float32), pool_pages, device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_decode (head_dim={head_dim}, splits={n_splits})")
     return out
 
@@ -591,7 +595,8 @@ CLUSTER_MERGE = _env_flag("REFLEX_B200_CLUSTER_MERGE", True)
 
 
 def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
-                      seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None) -> torch.Tensor:
+                      seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None,
+                      slopes=None) -> torch.Tensor:
     """bfloat16 tensor-core attention for a packed batch of sequences that
     each bring one or more rows (prefill, chunks, mixed steps)."""
     _chk(q, "q", torch.bfloat16)
@@ -607,7 +612,7 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
         S, int(max_new), nq, nkv, head_dim, int(window or 0), float(scale),
-        _chk(sink, "sink", torch.float32), _stream())
+        _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32), _stream())
     native.check(st, f"attention_prefill (head_dim={head_dim})")
     return out
 
@@ -633,26 +638,29 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
 
 
 def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_dim, window, scale,
-              sink=None):
+              sink=None, slopes=None):
     """Attention of the step's rows over their sequences' cached keys and
     values; picks the kernel for the dtype and the kind of step.  `sink`: one
-    float32 per query head whose exponential joins the softmax's denominator."""
+    float32 per query head whose exponential joins the softmax's denominator.
+    `slopes`: one float32 per query head; slope * (query position - key
+    position) is taken off every score (the tcgen05 prefill kernel has no such
+    term: with slopes the mma.sync one takes its head sizes too)."""
     fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if fast and batch.is_decode:
         pages = -(-min(batch.max_context, window or batch.max_context) // page_size) + (1 if window else 0)
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale,
-                                n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink)
-    if fast and nq // nkv <= 128 and head_dim in (64, 128):
+                                n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink, slopes=slopes)
+    if fast and nq // nkv <= 128 and head_dim in (64, 128) and slopes is None:
         return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                     batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
                                     nkv, head_dim, window, scale, sink)
     if fast and nq // nkv <= 128:
         return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                  batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                 nkv, head_dim, window, scale, sink)
+                                 nkv, head_dim, window, scale, sink, slopes)
     return attention_plain(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
-                           batch.row_slot, nq, nkv, head_dim, window, scale, sink)
+                           batch.row_slot, nq, nkv, head_dim, window, scale, sink, slopes)
 
 
 # ------------------------------------------------- further norms and embedding terms
@@ -812,43 +820,60 @@ def mlstm_out(num, den, proj, g_off: int, weight, eps: float, heads: int, vdim: 
 
 
 # ------------------------------------------------------- mixture of experts
-MOE_ACTIVATIONS = {"relu2": 0, "silu": 1}
+MOE_ACTIVATIONS = {"relu2": 0, "silu": 1, "glu_clamped": 2}
 
 
-def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+MOE_SCORES = {"softmax_top": 0, "sigmoid": 1}
+
+
+def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, experts: Optional[int] = None,
+              scores: str = "softmax_top"):
     """Router logits float32 [R, experts] (+ bias) -> ids int32 [R, top], the
-    experts with the largest logits, and weights float32 [R, top], the softmax
-    over the chosen logits only."""
+    experts with the largest logits, and weights float32 [R, top]: the softmax
+    over the chosen logits only ("softmax_top"), or each chosen logit's sigmoid
+    as it is ("sigmoid").  With `experts` only the first that many columns of
+    `logits` are router logits (the rest belongs to the caller)."""
     R, E = logits.shape
+    ld = E
+    E = E if experts is None else int(experts)
     ids = _new((R, top), torch.int32, logits.device)
     wts = _new((R, top), torch.float32, logits.device)
-    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32), _chk(bias, "bias", torch.float32),
-                                    ids.data_ptr(), wts.data_ptr(), R, E, int(top), _stream())
+    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32), ld, _chk(bias, "bias", torch.float32),
+                                    ids.data_ptr(), wts.data_ptr(), R, E, int(top), MOE_SCORES[scores], _stream())
     native.check(st, f"moe_route (experts={E}, top={top})")
     return ids, wts
 
 
 def moe_experts(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
-                wts: torch.Tensor, activation: str = "relu2") -> torch.Tensor:
+                wts: torch.Tensor, activation: str = "relu2", weight_input: bool = False,
+                alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
     """sum_k wts[r, k] down[e] act(up[e] x[r]), e = ids[r, k]; up [experts, ff,
     width], down [experts, width, ff]; float32 [R, width].  Every (row, choice)
     reads its expert's matrices itself: the form for a few rows, and the exact
-    one in 32-bit."""
+    one in 32-bit.  "glu_clamped": `up` is [experts, 2 ff, width], an expert's
+    gate rows and then its up rows, and act is the clamped gated form with
+    `alpha` and `limit` (`glu_clamped`).  `weight_input`: the weight multiplies
+    the expert's input instead of its output, sum_k down[e] act(up[e] (wts[r, k]
+    x[r]))."""
     R, width = x.shape
     E, ff, _w = up.shape
+    gated = activation == "glu_clamped"
+    if gated:
+        ff //= 2
     top = ids.shape[1]
+    in_scale, out_wts = (wts, None) if weight_input else (None, wts)
     if x.dtype == torch.bfloat16 and MOE_GROUPED and R >= MOE_GROUPED_MIN_ROWS:
         # captured steps too, as long as the library's grouped product (no wait for the host) is there
         if not torch.cuda.is_current_stream_capturing() or (_GROUPED_MM[0] and width % 8 == 0 and ff % 8 == 0):
-            return moe_experts_grouped(x, up, down, ids, wts, activation)
+            return moe_experts_grouped(x, up, down, ids, wts, activation, weight_input, alpha, limit)
     act = _new((R * top, ff), x.dtype, x.device)
     st = native.lib().rfx_moe_up(_chk(x, "x"), _chk(up, "up", x.dtype), _chk(ids, "ids", torch.int32),
-                                 act.data_ptr(), dt_code(x.dtype), R, top, ff, width,
-                                 MOE_ACTIVATIONS[activation], _stream())
+                                 _chk(in_scale, "wts", torch.float32), act.data_ptr(), dt_code(x.dtype), R, top,
+                                 ff, width, MOE_ACTIVATIONS[activation], float(alpha), float(limit), _stream())
     native.check(st, "moe_up")
     y = _new((R, width), torch.float32, x.device)
     st = native.lib().rfx_moe_down(act.data_ptr(), _chk(down, "down", x.dtype), ids.data_ptr(),
-                                   _chk(wts, "wts", torch.float32), y.data_ptr(), dt_code(x.dtype), R, top,
+                                   _chk(out_wts, "wts", torch.float32), y.data_ptr(), dt_code(x.dtype), R, top,
                                    ff, width, _stream())
     native.check(st, "moe_down")
     return y
@@ -862,7 +887,8 @@ MOE_GROUPED_MIN_ROWS = _env_int("REFLEX_B200_MOE_GROUPED_MIN_ROWS", 2, 1, 1 << 3
 
 
 def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
-                        wts: torch.Tensor, activation: str = "relu2") -> torch.Tensor:
+                        wts: torch.Tensor, activation: str = "relu2", weight_input: bool = False,
+                        alpha: float = 1.0, limit: float = 0.0) -> torch.Tensor:
     """The same sum for many bfloat16 rows (prefill): the (row, choice) pairs are
     placed expert by expert on the device, each expert's block of rows goes
     through its two matrices as library products (where the dense layers use
@@ -871,24 +897,35 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
     results are summed in the order of their rank."""
     R, width = x.shape
     E, ff, _w = up.shape
+    gated = activation == "glu_clamped"
+    if gated:
+        ff //= 2
     top = ids.shape[1]
     n = R * top
     lib = native.lib()
+    in_scale, out_wts = (wts, None) if weight_input else (None, wts)
+
+    def activate(a):
+        """The experts' activation on the up product's rows: in place, or (gated) [n, 2 ff] -> [n, ff]."""
+        if gated:
+            return glu_clamped(a, alpha, limit)
+        native.check(lib.rfx_moe_activation(a.data_ptr(), dt_code(a.dtype), a.numel(),
+                                            MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
+        return a
+
     offsets = _new((E + 1,), torch.int32, x.device)
     place = _new((n,), torch.int32, x.device)
     native.check(lib.rfx_moe_group(_chk(ids, "ids", torch.int32), n, E, offsets.data_ptr(), place.data_ptr(),
                                    _stream()), "moe_group")
     xg = _new((n, width), x.dtype, x.device)
-    native.check(lib.rfx_moe_gather(_chk(x, "x"), place.data_ptr(), xg.data_ptr(), dt_code(x.dtype), n, top,
-                                    width, _stream()), "moe_gather")
+    native.check(lib.rfx_moe_gather(_chk(x, "x"), place.data_ptr(), _chk(in_scale, "wts", torch.float32),
+                                    xg.data_ptr(), dt_code(x.dtype), n, top, width, _stream()), "moe_gather")
     grouped = getattr(torch, "_grouped_mm", None) if _GROUPED_MM[0] else None
     if grouped is not None and width % 8 == 0 and ff % 8 == 0:
         # the library's grouped product reads the experts' offsets on the device: no wait for the host
         try:
             ends = offsets[1:]
-            act = grouped(xg, up.transpose(1, 2), offs=ends)
-            native.check(lib.rfx_moe_activation(act.data_ptr(), dt_code(act.dtype), act.numel(),
-                                                MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
+            act = activate(grouped(xg, up.transpose(1, 2), offs=ends))
             try:  # 32-bit results where the library gives them: the weighted sum then rounds once
                 yg = grouped(act, down.transpose(1, 2), offs=ends, out_dtype=torch.float32) if _GROUPED_MM[1] else None
             except (RuntimeError, TypeError, NotImplementedError):
@@ -902,28 +939,175 @@ def moe_experts_grouped(x: torch.Tensor, up: torch.Tensor, down: torch.Tensor, i
         if yg is not None:
             y = _new((R, width), torch.float32, x.device)
             native.check(lib.rfx_moe_combine(_chk(yg, "yg"), dt_code(yg.dtype), place.data_ptr(),
-                                             _chk(wts, "wts", torch.float32), y.data_ptr(), R, top, width,
+                                             _chk(out_wts, "wts", torch.float32), y.data_ptr(), R, top, width,
                                              _stream()), "moe_combine")
             return y
     off = offsets.tolist()  # the one wait for the device
-    act = _new((n, ff), x.dtype, x.device)
+    act = _new((n, up.shape[1]), x.dtype, x.device)
     for e in range(E):
         if off[e + 1] > off[e]:
             torch.mm(xg[off[e]:off[e + 1]], up[e].t(), out=act[off[e]:off[e + 1]])
-    native.check(lib.rfx_moe_activation(act.data_ptr(), dt_code(act.dtype), act.numel(),
-                                        MOE_ACTIVATIONS[activation], _stream()), "moe_activation")
+    act = activate(act)
     yg = _new((n, width), torch.float32, x.device)
     for e in range(E):
         if off[e + 1] > off[e]:
             torch.mm(act[off[e]:off[e + 1]], down[e].t(), out_dtype=torch.float32, out=yg[off[e]:off[e + 1]])
     y = _new((R, width), torch.float32, x.device)
     native.check(lib.rfx_moe_combine(yg.data_ptr(), dt_code(yg.dtype), place.data_ptr(),
-                                     _chk(wts, "wts", torch.float32), y.data_ptr(), R, top, width, _stream()),
+                                     _chk(out_wts, "wts", torch.float32), y.data_ptr(), R, top, width, _stream()),
                  "moe_combine")
     return y
 
 
 _GROUPED_MM = [True, True]  # whether the library's grouped product is tried, and its 32-bit output
+
+
+# ------------------------------------------- clamped gated activation, row gates
+def glu_clamped(gate_up: torch.Tensor, alpha: float, limit: float, alternating: bool = False) -> torch.Tensor:
+    """[R, 2I] -> g' sigmoid(alpha g') (u' + 1), [R, I], with g' = min(g, limit)
+    and u' = clamp(u, -limit, limit).  A row holds the gates in its first half
+    and the ups in its second, or (`alternating`) gate_i at 2i and up_i at 2i + 1."""
+    R, two_i = gate_up.shape
+    I = two_i // 2
+    out = _new((R, I), gate_up.dtype, gate_up.device)
+    st = native.lib().rfx_glu_clamped(_chk(gate_up, "gate_up"), out.data_ptr(), dt_code(gate_up.dtype), R, I,
+                                      1 if alternating else 0, float(alpha), float(limit), _stream())
+    native.check(st, "glu_clamped")
+    return out
+
+
+def row_gate_add_(y: torch.Tensor, rows: torch.Tensor, z: torch.Tensor, col: int) -> torch.Tensor:
+    """y[r] += sigmoid(z[r, col]) * rows[r]: y float32 [R, H], z float32 [R, *]."""
+    R, H = y.shape
+    st = native.lib().rfx_row_gate_add(_chk(y, "y", torch.float32), _chk(rows, "rows"), dt_code(rows.dtype),
+                                       _chk(z, "z", torch.float32), z.shape[1], int(col), R, H, _stream())
+    native.check(st, "row_gate_add")
+    return y
+
+
+# ------------------------------------------------------------ the residual stream
+def stream_concat(x: torch.Tensor, delta: Optional[torch.Tensor], x0: torch.Tensor,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """[x (+ delta) | x0] row by row, [R, 2H] in `out_dtype`: the input of a
+    product that mixes the stream with the embedding output."""
+    R, H = x.shape
+    out = _new((R, 2 * H), out_dtype, x.device)
+    st = native.lib().rfx_stream_concat(_chk(x, "x", torch.float32), _chk(delta, "delta"),
+                                        dt_code(delta.dtype) if delta is not None else 0,
+                                        _chk(x0, "x0", torch.float32), out.data_ptr(), dt_code(out_dtype), R, H,
+                                        _stream())
+    native.check(st, "stream_concat")
+    return out
+
+
+def keep_copy(x: torch.Tensor) -> torch.Tensor:
+    """A copy of `x` that lives for the whole step."""
+    out = _new(tuple(x.shape), x.dtype, x.device, keep=True)
+    out.copy_(x)
+    return out
+
+
+def logit_finish_(z: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """z <- z * scale, then cap * tanh(z / cap) when cap > 0; float32, in place."""
+    if scale == 1.0 and not cap:
+        return z
+    st = native.lib().rfx_logit_finish(_chk(z, "z", torch.float32), z.numel(), float(scale), float(cap or 0.0),
+                                       _stream())
+    native.check(st, "logit_finish")
+    return z
+
+
+def branch_norm_mean(a: torch.Tensor, a_bias: Optional[torch.Tensor], wa: torch.Tensor, b: torch.Tensor,
+                     wb: torch.Tensor, eps: float) -> torch.Tensor:
+    """((a + a_bias) / rms(a + a_bias) * wa + b / rms(b) * wb) / 2, float32 [R, H]:
+    two branches' outputs, each RMS-normed with its own weight, averaged."""
+    R, H = a.shape
+    out = _new((R, H), torch.float32, a.device)
+    st = native.lib().rfx_branch_norm_mean(_chk(a, "a", torch.float32), _chk(a_bias, "a_bias", torch.float32),
+                                           _chk(wa, "wa", torch.float32), _chk(b, "b", torch.float32),
+                                           _chk(wb, "wb", torch.float32), float(eps), out.data_ptr(), R, H,
+                                           _stream())
+    native.check(st, "branch_norm_mean")
+    return out
+
+
+# ------------------------------------------- short convolutions, gated recurrence
+def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], weight: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch) -> torch.Tensor:
+    """A causal convolution over time of columns [col0, col0 + channels) of
+    `proj` (float32 [R, ld]) plus `bias`, one filter a channel (`weight`
+    float32 [channels, taps], the last tap on the current token) plus
+    `conv_bias`; what lies before a step's rows comes from `state` ([slots, n]
+    float32, whose first (taps - 1) * channels floats are the sequence's last
+    inputs, oldest first).  float32 [R, channels]."""
+    R = proj.shape[0]
+    taps = weight.shape[1]
+    out = _new((R, channels), torch.float32, proj.device)
+    st = native.lib().rfx_short_conv(
+        _chk(proj, "proj", torch.float32), proj.shape[1], int(col0), _chk(bias, "bias", torch.float32),
+        _chk(weight, "weight", torch.float32), _chk(conv_bias, "conv_bias", torch.float32), taps,
+        _chk(state, "state", torch.float32), state.stride(0) if state is not None else 0,
+        _chk(batch.row_slot, "row_slot", torch.int32), out.data_ptr(), R, channels, _stream())
+    native.check(st, f"short_conv (taps={taps})")
+    return out
+
+
+def conv_state_update(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], taps: int,
+                      state: torch.Tensor, batch) -> None:
+    """After a step's rows have been convolved: the sequences' new last taps - 1
+    inputs into `state`."""
+    if taps <= 1:
+        return
+    st = native.lib().rfx_conv_state_update(
+        _chk(proj, "proj", torch.float32), proj.shape[1], int(col0), _chk(bias, "bias", torch.float32), int(taps),
+        _chk(state, "state", torch.float32), state.stride(0), _chk(batch.seq_slot, "seq_slot", torch.int32),
+        _chk(batch.seq_row0, "seq_row0", torch.int32), batch.seq_slot.numel(), channels, _stream())
+    native.check(st, "conv_state_update")
+
+
+def conv_qkv_post(proj: torch.Tensor, bias: Optional[torch.Tensor], weight: torch.Tensor,
+                  state: Optional[torch.Tensor], batch, k_pages, v_pages, page_table, page_size: int, nq: int,
+                  nkv: int, dim: int, vdim: int, pad: int, temp_coef: float, temp_every: int, writes_cache: bool,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """The stacked q | k | v columns of `proj` (float32) plus `bias` through
+    their short convolutions (`weight` float32 [channels, taps]); q times the
+    temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p, out as
+    [R, nq * pad]; k and v into the cache at the rows' positions, heads `pad`
+    wide (zeros beyond `dim` and `vdim`)."""
+    R = proj.shape[0]
+    taps = weight.shape[1]
+    q = _new((R, nq * pad), out_dtype, proj.device)
+    st = native.lib().rfx_conv_qkv_post(
+        _chk(proj, "proj", torch.float32), proj.shape[1], _chk(bias, "bias", torch.float32),
+        _chk(weight, "weight", torch.float32), taps, _chk(state, "state", torch.float32),
+        state.stride(0) if state is not None else 0, _chk(batch.row_pos, "row_pos", torch.int32),
+        _chk(batch.row_slot, "row_slot", torch.int32), q.data_ptr(), _chk(k_pages, "k_pages", out_dtype),
+        _chk(v_pages, "v_pages", out_dtype), dt_code(out_dtype), _chk(page_table, "page_table", torch.int32),
+        page_table.shape[1], page_size, R, nq, nkv, dim, vdim, pad, float(temp_coef), int(temp_every),
+        1 if writes_cache else 0, _stream())
+    native.check(st, f"conv_qkv_post (dim={dim}, vdim={vdim})")
+    return q
+
+
+def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.Tensor, decay_scale: float,
+               proj: torch.Tensor, y_off: int, y_bias, state: torch.Tensor, state_off: int, batch, blocks: int,
+               out_dtype: torch.dtype) -> torch.Tensor:
+    """The gated linear recurrence over the step's rows, sequence by sequence
+    (csrc/rglru.cu): `u` float32 [R, W] its input, `gates` float32 [R, blocks,
+    2 W / blocks] the two gates' pre-activations, `proj` holds the other
+    branch's pre-activation at column `y_off`; the running S is `state[slot,
+    state_off : state_off + W]`.  Returns S * gelu_tanh(y), [R, W]."""
+    R, W = u.shape
+    out = _new((R, W), out_dtype, u.device)
+    st = native.lib().rfx_rglru_scan(
+        _chk(u, "u", torch.float32), _chk(gates, "gates", torch.float32), _chk(r_bias, "r_bias", torch.float32),
+        _chk(i_bias, "i_bias", torch.float32), _chk(lam, "lam", torch.float32), float(decay_scale),
+        _chk(proj, "proj", torch.float32), proj.shape[1], int(y_off), _chk(y_bias, "y_bias", torch.float32),
+        _chk(state, "state", torch.float32), state.stride(0), int(state_off),
+        _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
+        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), W, int(blocks), _stream())
+    native.check(st, f"rglru_scan (width={W}, blocks={blocks})")
+    return out
 
 
 # ------------------------------------------------------------------ sampling

@@ -40,16 +40,17 @@ _SIGNATURES = {
                      c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
                      c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "rfx_attention_plain": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
-                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p,
+                            c_void_p],
     "rfx_attention_decode": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                             c_longlong, c_void_p, c_void_p],
+                             c_void_p, c_longlong, c_void_p, c_void_p],
     "rfx_attention_decode_cluster": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                     c_longlong, c_void_p, c_void_p],
+                                     c_void_p, c_longlong, c_void_p, c_void_p],
     "rfx_attention_prefill": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                              c_float, c_void_p, c_void_p],
+                              c_float, c_void_p, c_void_p, c_void_p],
     "rfx_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
@@ -72,14 +73,31 @@ _SIGNATURES = {
                         c_void_p],
     "rfx_mlstm_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
                       c_int, c_int, c_void_p],
-    "rfx_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
-    "rfx_moe_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_up": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                   c_float, c_float, c_void_p],
     "rfx_moe_down": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                      c_void_p],
     "rfx_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
-    "rfx_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_moe_gather": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "rfx_moe_activation": [c_void_p, c_int, c_longlong, c_int, c_void_p],
     "rfx_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_short_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
+                       c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "rfx_conv_qkv_post": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+                          c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "rfx_conv_state_update": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
+                              c_int, c_int, c_void_p],
+    "rfx_rglru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                       c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                       c_int, c_int, c_void_p],
+    "rfx_branch_norm_mean": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                             c_void_p],
+    "rfx_glu_clamped": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "rfx_row_gate_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_stream_concat": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "rfx_logit_finish": [c_void_p, c_longlong, c_float, c_float, c_void_p],
     "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],
     "rfx_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p],
     "rfx_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

@@ -14,4 +14,5 @@ from .registry import (  # noqa: F401
     register_norm,
     register_position,
 )
-from . import norm, rope, mlp, attention, block, embedding, latent_attention, mlstm, moe  # noqa: F401,E402  (registers the parts)
+from . import norm, rope, mlp, attention, block, embedding, latent_attention, mlstm, moe  # noqa: F401,E402
+from . import conv_attention, rglru, pair  # noqa: F401,E402  (registers the parts)

@@ -1,7 +1,8 @@
 """Block arrangements: how a layer's parts are wired around the residual.
 
 "prenorm": h += mixer(norm1(h)); h += ffn(norm2(h))
-(src/model/dense.rs:1441-1484).  The residual stream is 32-bit; each add is
+(src/model/dense.rs:1441-1484).  "parallel": n = norm1(h); h += mixer(n) + ffn(n),
+one norm that both sublayers read.  The residual stream is 32-bit; each add is
 fused into the norm that follows it, so a block hands its last delta on as
 `pending` and the next block's (or the model's final) norm adds it
 (src/model/decode_step.rs:199-210, 293-300).
@@ -113,3 +114,61 @@ class PreNormBlock:
         else:
             f = self.feed_forward.forward(x)
         return hidden, f
+
+
+@register_block("parallel")
+class ParallelBlock(PreNormBlock):
+    """n = norm(h); h += mixer(n) + ffn(n): one norm, both sublayers read its
+    output, their sum is the layer's delta.  The spec's `feed_forward_norm` is
+    None; a layer without a feed-forward is h += mixer(norm(h))."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.mixer_norm = NORMS.get(spec.mixer_norm.kind)(spec.mixer_norm, dtype, device)
+        self.mixer = MIXERS.get(spec.mixer.kind)(spec.mixer, dtype, device)
+        self.has_feed_forward = spec.feed_forward is not None
+        self.feed_forward_norm = None
+        self.feed_forward = (FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
+                             if self.has_feed_forward else None)
+
+    fusable_first_norm = None  # its mixers take plain normed rows
+
+    @property
+    def capturable(self) -> bool:
+        parts = [self.mixer_norm, self.mixer] + ([self.feed_forward] if self.has_feed_forward else [])
+        return all(bool(getattr(p, "capturable", False)) for p in parts)
+
+    @classmethod
+    def tensor_names(cls, spec: LayerSpec) -> Dict[str, Tuple[str, str, TensorInfo]]:
+        import dataclasses
+
+        # the names of a pre-norm layer whose feed-forward has no norm of its own
+        out = PreNormBlock.tensor_names(dataclasses.replace(spec, feed_forward=None))
+        if spec.feed_forward is not None:
+            names = names_dict(spec.feed_forward.names)
+            for role, info in FEED_FORWARDS.get(spec.feed_forward.kind).tensor_specs(spec.feed_forward).items():
+                base, _, index = role.partition("#")
+                suffix = names.get(base, base)
+                out[spec.prefix + (suffix.format(expert=index) if index else suffix)] = ("feed_forward", role, info)
+        return out
+
+    def bind(self, by_part: Dict[str, Dict[str, torch.Tensor]]) -> None:
+        self.mixer_norm.bind(by_part.get("mixer_norm", {}))
+        self.mixer.bind(by_part.get("mixer", {}))
+        if self.has_feed_forward:
+            self.feed_forward.bind(by_part.get("feed_forward", {}))
+
+    def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
+        from .. import ops
+
+        if isinstance(pending, ops.NormedInput):
+            pending = None  # the stream already holds the sum; this block's parts want plain normed rows
+        x = self.mixer_norm(hidden, delta=pending)
+        ops.prof_mark("norm")
+        delta = self.mixer.forward(x, ctx)
+        if self.has_feed_forward:
+            if getattr(self.feed_forward, "supports_onto", False):
+                delta = self.feed_forward.forward(x, onto=delta)
+            else:
+                delta = ops.add_(delta, self.feed_forward.forward(x))
+        return hidden, delta

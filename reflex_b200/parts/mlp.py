@@ -65,3 +65,50 @@ class SwiGLU:
         out = ops.linear(act, self.down, out_dtype=torch.float32)
         ops.prof_mark("ffn_down")
         return out
+
+
+@register_feed_forward("glu_clamped")
+class ClampedGLU:
+    """The clamped gated feed-forward: g = min(W_g x, limit), u = clamp(W_u x,
+    -limit, limit), out = W_d (g * sigmoid(alpha g) * (u + 1)); `alpha` and
+    `limit` are the spec's parameters.  Gate and up are one woven matrix, as in
+    `SwiGLU`.  `forward(x, onto=delta)` adds the result onto a 32-bit delta
+    another part made from the same input (a mixer beside it) and returns it."""
+
+    capturable = True
+
+    def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.alpha = float(spec.param("alpha", 1.0))
+        self.limit = float(spec.param("limit"))
+        self.gate_up = None
+        self.down = None
+
+    @classmethod
+    def tensor_specs(cls, spec: FeedForwardSpec) -> Dict[str, TensorInfo]:
+        return SwiGLU.tensor_specs(spec)
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        def dev(t):
+            return t.to(device=self.device, dtype=self.dtype)
+
+        g, u = dev(tensors["gate_proj"]), dev(tensors["up_proj"])
+        self.gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
+        self.down = dev(tensors["down_proj"]).contiguous()
+
+    supports_onto = True
+
+    def forward(self, x, residual=None, onto=None):
+        act = ops.glu_clamped(ops.linear(x, self.gate_up), self.alpha, self.limit, alternating=True)
+        ops.prof_mark("ffn_gate_up")
+        if onto is not None:
+            # many bfloat16 rows: the product accumulates onto the 32-bit delta
+            if ops.linear_residual(act, self.down, onto, None) is not ops.ADDED:
+                ops.add_(onto, ops.linear(act, self.down, out_dtype=torch.float32))
+            ops.prof_mark("ffn_down")
+            return onto
+        out = ops.linear(act, self.down, out_dtype=torch.float32)
+        ops.prof_mark("ffn_down")
+        return out

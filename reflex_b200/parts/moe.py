@@ -7,6 +7,17 @@ square of relu ("relu2") or silu; the output is the weighted sum of the chosen
 experts' outputs, summed in the order of their rank in 32-bit, so a row's
 result does not depend on what else is in the batch.  The experts' matrices
 are stacked at load: up [experts, ff, hidden], down [experts, hidden, ff].
+
+Variants, all by the spec's parameters.  `scores` "sigmoid": the chosen
+experts' weights are the sigmoids of their logits, not renormalised.
+`activation` "glu_clamped": an expert is the clamped gated form
+W_down (g * sigmoid(alpha g) * (u + 1)) with g = min(W_gate x, limit) and
+u = clamp(W_up x, -limit, limit) (its gate and up matrices stacked [experts,
+2 ff, hidden]).  `weight_input`: the weight multiplies the expert's input, the
+output is sum_k expert_k(w_k x).  `shared_ff` > 0: a shared expert of that
+width (the same clamped gated form with `shared_limit`) runs for every row and
+is added times sigmoid(w_sg . x), one number a row; its gate's row rides along
+as one more row of the router's matrix.
 """
 
 from __future__ import annotations
@@ -31,7 +42,14 @@ class MixtureOfExperts:
         self.experts = int(spec.param("experts"))
         self.top = int(spec.param("top"))
         self.activation = str(spec.param("activation", "relu2"))
+        self.scores = str(spec.param("scores", "softmax_top"))
+        self.weight_input = bool(spec.param("weight_input", False))
+        self.alpha = float(spec.param("alpha", 1.0))
+        self.limit = float(spec.param("limit", 0.0))
+        self.shared_ff = int(spec.param("shared_ff", 0) or 0)
+        self.shared_limit = float(spec.param("shared_limit", 0.0))
         self.router = self.router_bias = self.up = self.down = None
+        self.shared_gate_up = self.shared_down = None
 
     @classmethod
     def tensor_specs(cls, spec: FeedForwardSpec) -> Dict[str, TensorInfo]:
@@ -39,9 +57,16 @@ class MixtureOfExperts:
         out = {"router": TensorInfo((E, H), "matrix")}
         if spec.param("router_bias", False):
             out["router_bias"] = TensorInfo((E,), "bias")
+        gated = spec.param("activation") == "glu_clamped"
         for e in range(E):  # role#index: the checkpoint names every expert's tensors
+            if gated:
+                out[f"expert_gate#{e}"] = TensorInfo((I, H), "matrix")
             out[f"expert_up#{e}"] = TensorInfo((I, H), "matrix")
             out[f"expert_down#{e}"] = TensorInfo((H, I), "matrix")
+        S = int(spec.param("shared_ff", 0) or 0)
+        if S:
+            out.update({"shared_gate": TensorInfo((S, H), "matrix"), "shared_up": TensorInfo((S, H), "matrix"),
+                        "shared_down": TensorInfo((H, S), "matrix"), "shared_sg": TensorInfo((1, H), "matrix")})
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -51,13 +76,28 @@ class MixtureOfExperts:
         self.router = dev(tensors["router"]).contiguous()
         b = tensors.get("router_bias")
         self.router_bias = None if b is None else b.to(device=self.device, dtype=torch.float32).contiguous()
-        self.up = torch.stack([dev(tensors[f"expert_up#{e}"]) for e in range(self.experts)]).contiguous()
+        if self.activation == "glu_clamped":  # an expert's gate rows, then its up rows
+            self.up = torch.stack([torch.cat([dev(tensors[f"expert_gate#{e}"]), dev(tensors[f"expert_up#{e}"])])
+                                   for e in range(self.experts)]).contiguous()
+        else:
+            self.up = torch.stack([dev(tensors[f"expert_up#{e}"]) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([dev(tensors[f"expert_down#{e}"]) for e in range(self.experts)]).contiguous()
+        if self.shared_ff:
+            self.router = torch.cat([self.router, dev(tensors["shared_sg"]).reshape(1, -1)]).contiguous()
+            g, u = dev(tensors["shared_gate"]), dev(tensors["shared_up"])
+            self.shared_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
+            self.shared_down = dev(tensors["shared_down"]).contiguous()
 
     def forward(self, x, residual=None):
-        logits = ops.linear(x, self.router, out_dtype=torch.float32)
-        ids, wts = ops.moe_route(logits, self.router_bias, self.top)
+        logits = ops.linear(x, self.router, out_dtype=torch.float32)  # [rows, experts (+ the shared gate)]
+        ids, wts = ops.moe_route(logits, self.router_bias, self.top, experts=self.experts, scores=self.scores)
         ops.prof_mark("moe_router")
-        out = ops.moe_experts(x, self.up, self.down, ids, wts, self.activation)
+        out = ops.moe_experts(x, self.up, self.down, ids, wts, self.activation, self.weight_input, self.alpha,
+                              self.limit)
         ops.prof_mark("moe_experts")
+        if self.shared_ff:
+            act = ops.glu_clamped(ops.linear(x, self.shared_gate_up), self.alpha, self.shared_limit,
+                                  alternating=True)
+            ops.row_gate_add_(out, ops.linear(act, self.shared_down, out_dtype=torch.float32), logits, self.experts)
+            ops.prof_mark("moe_shared")
         return out

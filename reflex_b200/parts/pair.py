@@ -1,0 +1,87 @@
+"""Two mixers side by side on the same input.
+
+out = (norm_l(left(h)) + norm_r(right(h))) / 2, each branch's output over its
+root mean square (over the model width) times a weight of its own.  The two
+branches are registered mixers of any kind, named by the spec's `left` and
+`right` parameters; what they keep in the cache is asked for together (a tuple
+of their specs) and handed to each in turn.  A branch may return `(delta,
+bias)`: a bias of its last product that this part's kernel adds before the
+norm.
+"""
+
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import ops
+from ..config.spec import MixerSpec, names_dict
+from .registry import MIXERS, TensorInfo, register_mixer
+
+
+def _as_tuple(spec):
+    if spec is None:
+        return ()
+    return tuple(spec) if isinstance(spec, (tuple, list)) else (spec,)
+
+
+@register_mixer("pair")
+class PairMixer:
+    SIDES = ("left", "right")
+
+    def __init__(self, spec: MixerSpec, dtype: torch.dtype, device):
+        self.spec = spec
+        self.dtype = dtype
+        self.device = device
+        self.eps = float(spec.param("eps"))
+        self.branches = [MIXERS.get(spec.param(side).kind)(spec.param(side), dtype, device) for side in self.SIDES]
+        self.weights = [None, None]
+
+    @property
+    def capturable(self) -> bool:
+        return all(bool(getattr(b, "capturable", False)) for b in self.branches)
+
+    @classmethod
+    def tensor_specs(cls, spec: MixerSpec) -> Dict[str, TensorInfo]:
+        out = {}
+        for side in cls.SIDES:
+            sub = spec.param(side)
+            for role, info in MIXERS.get(sub.kind).tensor_specs(sub).items():
+                out[f"{side}/{role}"] = info
+            out[f"{side}_out"] = TensorInfo((spec.hidden_size,), "norm")
+        return out
+
+    def cache_spec(self):
+        """Everything the two branches keep, the left one's parts first."""
+        return tuple(p for b in self.branches for p in _as_tuple(b.cache_spec() if hasattr(b, "cache_spec") else None))
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for i, (side, branch) in enumerate(zip(self.SIDES, self.branches)):
+            branch.bind({role[len(side) + 1:]: t for role, t in tensors.items() if role.startswith(side + "/")})
+            self.weights[i] = tensors[f"{side}_out"].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def forward(self, x, ctx):
+        from ..engine.model import RunContext
+
+        views = list(ctx.parts) if ctx.parts is not None else [v for v in (ctx.kv, ctx.state) if v is not None]
+        outs = []
+        for branch in self.branches:
+            n = len(_as_tuple(branch.cache_spec() if hasattr(branch, "cache_spec") else None))
+            mine, views = views[:n], views[n:]
+            sub = RunContext(batch=ctx.batch, writes_cache=ctx.writes_cache, entry=ctx.entry, parts=mine)
+            sub.kv = next((v for v in mine if not isinstance(v, torch.Tensor)), None)
+            sub.state = next((v for v in mine if isinstance(v, torch.Tensor)), None)
+            r = branch.forward(x, sub)
+            outs.append(r if isinstance(r, tuple) else (r, None))
+        (a, a_bias), (b, b_bias) = outs
+        if b_bias is not None:  # the kernel takes one bias: give it the branch that has one
+            if a_bias is not None:
+                b = b + b_bias
+            else:
+                out = ops.branch_norm_mean(b, b_bias, self.weights[1], a, self.weights[0], self.eps)
+                ops.prof_mark("pair_out")
+                return out
+        out = ops.branch_norm_mean(a, a_bias, self.weights[0], b, self.weights[1], self.eps)
+        ops.prof_mark("pair_out")
+        return out

@@ -42,6 +42,7 @@ class TensorInfo:
     # "table":  an embedding table, same
     # "norm":   a norm's weight, kept 32-bit, drawn 1 + U(-0.1, 0.1)
     # "bias":   a bias or another small vector, kept 32-bit, drawn U(-0.5, 0.5)
+    # "filter": the taps of a short convolution, kept 32-bit, drawn U(-0.6, 0.6)
     role: str
     optional: bool = False
 

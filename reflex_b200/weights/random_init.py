@@ -75,7 +75,8 @@ def draw_host(key: int, n: int, kind: str, a: float, b: float, first: int = 0) -
     return v.astype(np.float32)
 
 
-ROLE_DRAWS = {"norm": ("uniform", 0.9, 1.1), "bias": ("uniform", -0.5, 0.5)}  # every other role: N(0, 0.02)
+# every other role: N(0, 0.02); "filter": a short convolution's taps, kept 32-bit like a bias
+ROLE_DRAWS = {"norm": ("uniform", 0.9, 1.1), "bias": ("uniform", -0.5, 0.5), "filter": ("uniform", -0.6, 0.6)}
 
 
 def draw(name: str, shape, role: str, seed: int, device="cpu", dtype: torch.dtype = torch.float32) -> torch.Tensor:
@@ -149,6 +150,6 @@ def random_model_on_device(config: Dict[str, Any], seed: int, dtype: torch.dtype
     tensors = {}
     for name, (_where, info) in expected_tensors(spec).items():
         tensors[name] = draw(name, info.shape, info.role, seed, device,
-                             torch.float32 if info.role in ("norm", "bias") else store)
+                             torch.float32 if info.role in ("norm", "bias", "filter") else store)
     model.bind(tensors)
     return model
