@@ -279,6 +279,26 @@ def kegasun_config(z):
             "layers": layers}
 
 
+def pakarax_config(z):
+    """Pakarax at the sizes of `z`: every layer an attention (a quarter as many
+    key/value heads, filters of four taps) beside a gated linear recurrence of
+    the model's width, dense and routed feed-forwards in turn (the routed ones
+    with a shared expert); all layers form one pass of the loop, so that the
+    number of layer runs and the weights equal the models beside it."""
+    pair = {"type": "parallel",
+            "mixer": {"left": {"heads": z["heads"], "kv_heads": max(1, z["heads"] // 4), "dim": z["dim"],
+                               "vdim": z["dim"], "conv": 4, "scale": z["dim"] ** -0.5,
+                               "q_temp": {"coef": 0.3, "every": 128}},
+                      "right": {"width": z["width"], "blocks": z["heads"], "conv": 4}}}
+    dense = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["expert_ff"], "limit": 7.0}}
+    layers = [dict(pair, mlp=(dense, moe)[i % 2]) for i in range(z["layers"])]
+    return {"architecture": "Pakarax", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "logit_scale": 1.0, "logit_softcap": 30.0, "loop": {"start": 0, "stop": z["layers"], "times": 1},
+            "layers": layers}
+
+
 def qwen3_config_like(z):
     cfg = dict(QWEN3_8B)
     cfg.update({"num_hidden_layers": z["layers"], "hidden_size": z["width"], "num_attention_heads": z["heads"],
@@ -289,8 +309,10 @@ def qwen3_config_like(z):
 
 
 def design_comparison(args) -> int:
-    """Prefill and decode throughput of the Kegasun design beside Qwen3 at equal
-    sizes, with every phase's time in a prefill and in a decode step."""
+    """Prefill and decode throughput of a design (`--design`) beside Qwen3 at
+    equal sizes (and, for Pakarax, beside Kegasun too: the model with a
+    recurrence and experts), with every phase's time in a prefill and in a
+    decode step."""
     import torch
 
     from reflex_b200 import ops
@@ -300,7 +322,11 @@ def design_comparison(args) -> int:
     pk = peaks()
     torch.cuda.set_device(0)
     T, B, P, steps = PREFILL_TOKENS, args.batch, PROMPT, max(16, min(args.steps, 64))
-    out = {"metric": "prefill and decode tokens/s, Kegasun beside Qwen3 at equal sizes", "unit": "tokens/s",
+    mine = args.design
+    beside = [("qwen3", qwen3_config_like)] + ([("kegasun", kegasun_config)] if mine == "pakarax" else [])
+    mine_config = {"kegasun": kegasun_config, "pakarax": pakarax_config}[mine]
+    out = {"metric": f"prefill and decode tokens/s, {mine} beside " + " and ".join(n for n, _ in beside)
+                     + " at equal sizes", "unit": "tokens/s",
            "dtype": "bf16", "data": "synthetic: seeded uniform token ids, random-init weights",
            "prefill_tokens": T, "decode_batch": B, "decode_prompt": P, "decode_steps": steps,
            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"], "of": pk["source"]}, "sizes": {}}
@@ -308,7 +334,7 @@ def design_comparison(args) -> int:
     for name in names:
         z = DESIGN_SIZES[name]
         row = {}
-        for design, cfg in (("kegasun", kegasun_config(z)), ("qwen3", qwen3_config_like(z))):
+        for design, cfg in [(mine, mine_config(z))] + [(n, f(z)) for n, f in beside]:
             lm = random_model_on_device(cfg, 0, torch.bfloat16, "cuda:0")
             model = Model(lm, max_tokens=B * (P + steps + 128) + T + 256, max_batch=B)
             eng = model.engine
@@ -374,8 +400,10 @@ def design_comparison(args) -> int:
 
             gc.collect()
             torch.cuda.empty_cache()
-        row["prefill_ratio"] = row["kegasun"]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
-        row["decode_ratio"] = row["kegasun"]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
+        for other, _ in beside:
+            suffix = "" if other == "qwen3" else f"_vs_{other}"
+            row["prefill_ratio" + suffix] = row[mine]["prefill_tok_s"] / row[other]["prefill_tok_s"]
+            row["decode_ratio" + suffix] = row[mine]["decode_tok_s"] / row[other]["decode_tok_s"]
         out["sizes"][name] = row
     print(json.dumps(out))
     return 0
@@ -419,7 +447,7 @@ def main() -> int:
                     help="workloads beside the headline: 14b and 32b add their points (default: all)")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="prompt tokens before the decode steps")
     ap.add_argument("--context", type=int, default=CONTEXT, help="cache positions per sequence")
-    ap.add_argument("--design", default="", choices=["", "kegasun"],
+    ap.add_argument("--design", default="", choices=["", "kegasun", "pakarax"],
                     help="instead of the headline: this design beside Qwen3 at equal sizes (prefill, decode, phases)")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="with --design: which of the sizes " +
                     ", ".join(sorted(DESIGN_SIZES)))

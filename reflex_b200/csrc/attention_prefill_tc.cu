@@ -105,7 +105,11 @@ struct Smem {
     static constexpr int total(int D) { return q_bytes(D) + 2 * KV_STAGES * kv_bytes(D) + 1024; }
 };
 
-template <int D>
+// SLOPES: a linear distance bias, slope_h * (query position - key position) off
+// every score of head h; taken off the raw score as (slope / scale) * distance,
+// so that the scale's multiply-add in the exponent covers it.  Without it the
+// kernel's instructions are what they were.
+template <int D, bool SLOPES>
 __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const __grid_constant__ CUtensorMap map_k,
@@ -113,7 +117,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
                             const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                             const int* __restrict__ seq_new, const int* __restrict__ seq_row0,
                             __nv_bfloat16* __restrict__ out, int nq, int bq, int window,
-                            float scale_log2, const float* __restrict__ sink, int* __restrict__ err) {
+                            float scale_log2, const float* __restrict__ sink,
+                            const float* __restrict__ slopes, int* __restrict__ err) {
     static_assert(D == 64 || D == 128, "head sizes 64 and 128");
     constexpr int KB = D / 64;                 // 64-column blocks of a row
     constexpr int KV_BYTES = PAGE * D * 2;
@@ -271,6 +276,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
         const int row_pos = row_valid ? pos_first + row_p : -1;
         const int row_lo = (window > 0 && row_pos + 1 > window) ? row_pos + 1 - window : 0;
         const int lo_last = (window > 0 && pos_last + 1 > window) ? pos_last + 1 - window : 0;
+        // the row's head's slope in units of the raw score (a weight: read before any wait)
+        float slope_raw = 0.0f;
+        if constexpr (SLOPES) slope_raw = slopes[kvh * g + min(row_h, g - 1)] * 1.4426950408889634f / scale_log2;
         constexpr float RAISE = 8.0f;  // raise the reference maximum only past 2^8
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
@@ -298,6 +306,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q,
             // scheduler has nothing else to hide a dependent chain's latency with
             float s[PAGE];  // raw scores; the scale (positive) goes into the exponent's multiply-add
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if constexpr (SLOPES) {
+                const float d0 = (float)(row_pos - basej);  // distance of the page's first key
+#pragma unroll
+                for (int c = 0; c < PAGE; ++c)
+                    sr[c] = __float_as_uint(fmaf(-slope_raw, d0 - (float)c, __uint_as_float(sr[c])));
+            }
             if (all_visible) {
 #pragma unroll
                 for (int c = 0; c < PAGE; ++c) s[c] = __uint_as_float(sr[c]);
@@ -434,11 +448,11 @@ bool make_map_q(CUtensorMap* map, const void* base, int R, int nq, int D, int g,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int D>
+template <int D, bool SLOPES>
 int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long n_pages_total,
               const PagedKV& cache, const int* seq_slot, const int* seq_start, const int* seq_new,
               const int* seq_row0, void* out, int S, int max_new, int R, int nq, int window, float scale,
-              const float* sink, int* err, cudaStream_t s) {
+              const float* sink, const float* slopes, int* err, cudaStream_t s) {
     const int g = nq / cache.n_kv_heads;
     if (g > ROWS) return RFX_ERR_UNSUPPORTED;
     const int bq = ROWS / g;
@@ -448,14 +462,14 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
         !rfx::tma::make_map_rows64(&mv, v_pages, kv_rows, D, PAGE))
         return RFX_ERR_UNSUPPORTED;
     const size_t smem = Smem::total(D);
-    auto kernel = attention_prefill_tc_kernel<D>;
+    auto kernel = attention_prefill_tc_kernel<D, SLOPES>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     if ((max_new + bq - 1) / bq > 65535 || S > 65535) return RFX_ERR_UNSUPPORTED;
     dim3 grid(cache.n_kv_heads, S, (max_new + bq - 1) / bq);
     if (grid.y > 65535 || grid.z > 65535) return RFX_ERR_UNSUPPORTED;
     RFX_LAUNCH(kernel, grid, THREADS, smem, s, mq, mk, mv, cache, seq_slot, seq_start, seq_new, seq_row0,
-               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, err);
+               (__nv_bfloat16*)out, nq, bq, window, scale * 1.4426950408889634f, sink, slopes, err);
     return 0;
 }
 
@@ -464,6 +478,8 @@ int launch_tc(const void* q, const void* k_pages, const void* v_pages, long long
 // As rfx_attention_prefill, for head_dim 64 or 128.  `n_pages_total` is the
 // number of pages of the K/V store (for the TMA maps), R the number of rows of
 // q.  `err` is a device word that receives a code if a bounded wait ran out.
+// `slopes` (one float per query head, or null): slope * (query position - key
+// position) is taken off every score; needs scale > 0.
 // Tuning aid: 32 64-bit timestamps per CTA of the launches that follow (null
 // switches it off).
 extern "C" int rfx_attention_prefill_tc_trace(void* buffer, int ctas) {
@@ -478,19 +494,21 @@ extern "C" int rfx_attention_prefill_tc(const void* q, const void* k_pages, cons
                                         int page_size, const int* seq_slot, const int* seq_start,
                                         const int* seq_new, const int* seq_row0, void* out, int S,
                                         int max_new, int R, int nq, int nkv, int head_dim, int window,
-                                        float scale, const float* sink, int* err, void* stream) {
+                                        float scale, const float* sink, const float* slopes, int* err,
+                                        void* stream) {
     if (S <= 0 || max_new <= 0 || R <= 0) return 0;
     if (page_size != PAGE || nkv <= 0 || nq % nkv != 0) return RFX_ERR_BAD_ARG;
+    if (slopes && !(scale > 0.0f)) return RFX_ERR_UNSUPPORTED;  // the slopes ride on the scale's multiply-add
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_pages) |
          reinterpret_cast<uintptr_t>(v_pages)) & 15)
         return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, head_dim};
     cudaStream_t s = (cudaStream_t)stream;
-    if (head_dim == 64)
-        return launch_tc<64>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
-                             seq_row0, out, S, max_new, R, nq, window, scale, sink, err, s);
-    if (head_dim == 128)
-        return launch_tc<128>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new,
-                              seq_row0, out, S, max_new, R, nq, window, scale, sink, err, s);
+#define RFX_GO(DD, SL)                                                                                  \
+    launch_tc<DD, SL>(q, k_pages, v_pages, n_pages_total, cache, seq_slot, seq_start, seq_new, seq_row0, \
+                      out, S, max_new, R, nq, window, scale, sink, slopes, err, s)
+    if (head_dim == 64) return slopes ? RFX_GO(64, true) : RFX_GO(64, false);
+    if (head_dim == 128) return slopes ? RFX_GO(128, true) : RFX_GO(128, false);
+#undef RFX_GO
     return RFX_ERR_UNSUPPORTED;
 }

@@ -11,8 +11,19 @@
 // All of it is 32-bit; sqrt(1 - a^2) is taken as sqrt(-expm1(2 log a)), which
 // keeps its digits when a is close to one.  S lives in the cache's state
 // ([slot][...], at `state_off`), read when a step begins and stored when it
-// ends.  A thread owns one channel of one sequence and walks the step's rows
-// in order.
+// ends.
+//
+// Two kernels.  A few rows a sequence (decode): a thread owns one channel of
+// one sequence and walks the step's rows in order.  Many rows (prompts): the
+// recurrence is linear, S_t = a_t S_(t-1) + b_t, so a stretch of rows folds into
+// one pair (P, B) with S_end = P S_begin + B; a block owns 16 channels of a
+// sequence and takes 64 rows at a time, 16 groups of threads with 4 rows each:
+// every thread loads its rows, does all the gates' arithmetic and folds its 4
+// rows (keeping each row's own pair), the groups' pairs meet in shared memory,
+// every thread folds the groups before it onto the carried S, and then writes
+// its rows' outputs.  The loads and the exponentials of 64 rows run side by
+// side; only 16 multiply-adds a tile are in sequence.  Both kernels compute the
+// same function, rounded differently.
 #include "common.cuh"
 
 namespace {
@@ -62,18 +73,103 @@ rglru_scan_kernel(const float* __restrict__ u, const float* __restrict__ gates,
     *sp = S;
 }
 
+constexpr int CH_CHANNELS = 16, CH_GROUPS = 16, CH_ROWS = 4;  // 64 rows a tile
+
+template <typename TO>
+__global__ void __launch_bounds__(CH_CHANNELS * CH_GROUPS)
+rglru_chunk_kernel(const float* __restrict__ u, const float* __restrict__ gates,
+                   const float* __restrict__ r_bias, const float* __restrict__ i_bias,
+                   const float* __restrict__ lam, float decay_scale, const float* __restrict__ proj, int ld,
+                   int y_off, const float* __restrict__ y_bias, float* __restrict__ state, size_t slot_stride,
+                   size_t state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
+                   TO* __restrict__ out, int W, int K) {
+    __shared__ float fold_p[CH_GROUPS][CH_CHANNELS], fold_b[CH_GROUPS][CH_CHANNELS];
+    __shared__ float carry[2][CH_CHANNELS];
+    pdl_prologue();
+    const int s = blockIdx.x;
+    const int cl = threadIdx.x % CH_CHANNELS, grp = threadIdx.x / CH_CHANNELS;
+    const int c = blockIdx.y * CH_CHANNELS + cl;
+    const bool live = c < W;
+    const int cc = live ? c : W - 1;  // idle threads follow a real channel and store nothing
+    const int row0 = seq_row0[s], n = seq_row0[s + 1] - row0;
+    float* sp = state + (size_t)seq_slot[s] * slot_stride + state_off + cc;
+    const int b = cc / K, k = cc % K;
+    const size_t g_r = (size_t)b * 2 * K + k, g_i = g_r + K;
+    const float rb = r_bias ? r_bias[cc] : 0.0f, ib = i_bias ? i_bias[cc] : 0.0f;
+    const float yb = y_bias ? y_bias[cc] : 0.0f;
+    const float rate = -decay_scale * softplus_f(lam[cc]);
+    if (grp == 0) carry[0][cl] = *sp;
+    int cur = 0;
+    for (int tile = 0; tile < n; tile += CH_GROUPS * CH_ROWS) {
+        float P[CH_ROWS], B[CH_ROWS], Y[CH_ROWS];
+        float p = 1.0f, acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < CH_ROWS; ++j) {
+            const int t = tile + grp * CH_ROWS + j;
+            if (t < n) {
+                const size_t row = (size_t)(row0 + t);
+                const float uv = u[row * W + cc];
+                const float r = sigmoid_f(gates[row * 2 * W + g_r] + rb);
+                const float i = sigmoid_f(gates[row * 2 * W + g_i] + ib);
+                Y[j] = gelu_tanh_f(proj[row * ld + y_off + cc] + yb);
+                const float log_a = rate * r;
+                const float a = expf(log_a);
+                acc = fmaf(a, acc, sqrtf(-expm1f(2.0f * log_a)) * (i * uv));
+                p *= a;
+            } else {
+                Y[j] = 0.0f;
+            }
+            P[j] = p;
+            B[j] = acc;
+        }
+        fold_p[grp][cl] = p;
+        fold_b[grp][cl] = acc;
+        __syncthreads();
+        float S = carry[cur][cl];
+        for (int g2 = 0; g2 < grp; ++g2) S = fmaf(fold_p[g2][cl], S, fold_b[g2][cl]);
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < CH_ROWS; ++j) {
+                const int t = tile + grp * CH_ROWS + j;
+                if (t < n) st<TO>(out, (size_t)(row0 + t) * W + c, fmaf(P[j], S, B[j]) * Y[j]);
+            }
+        }
+        // the last group's end is the tile's; the other buffer, so that no thread still reads this one
+        if (grp == CH_GROUPS - 1) carry[cur ^ 1][cl] = fmaf(p, S, acc);
+        cur ^= 1;
+        __syncthreads();
+    }
+    if (live && grp == 0) *sp = carry[cur][cl];
+}
+
 }  // namespace
 
+// `chunked` != 0: the form for many rows a sequence (above)
 extern "C" int rfx_rglru_scan(const float* u, const float* gates, const float* r_bias, const float* i_bias,
                               const float* lam, float decay_scale, const float* proj, int ld, int y_off,
                               const float* y_bias, float* state, long long slot_stride, long long state_off,
                               const int* seq_slot, const int* seq_row0, int S, void* out, int out_dt, int W,
-                              int blocks, void* stream) {
+                              int blocks, int chunked, void* stream) {
     if (S <= 0 || W <= 0) return 0;
     if (blocks <= 0 || W % blocks != 0) return RFX_ERR_BAD_ARG;
     dim3 grid(S, (W + 127) / 128);
     cudaStream_t s = (cudaStream_t)stream;
     const int K = W / blocks;
+    if (chunked) {
+        dim3 cgrid(S, (W + CH_CHANNELS - 1) / CH_CHANNELS);
+        if (cgrid.y > 65535) return RFX_ERR_UNSUPPORTED;
+        if (out_dt == RFX_DT_F32)
+            RFX_LAUNCH(rglru_chunk_kernel<float>, cgrid, CH_CHANNELS * CH_GROUPS, 0, s, u, gates, r_bias, i_bias,
+                       lam, decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off,
+                       seq_slot, seq_row0, (float*)out, W, K);
+        else if (out_dt == RFX_DT_BF16)
+            RFX_LAUNCH(rglru_chunk_kernel<__nv_bfloat16>, cgrid, CH_CHANNELS * CH_GROUPS, 0, s, u, gates, r_bias,
+                       i_bias, lam, decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride,
+                       (size_t)state_off, seq_slot, seq_row0, (__nv_bfloat16*)out, W, K);
+        else
+            return RFX_ERR_BAD_ARG;
+        return 0;
+    }
     if (out_dt == RFX_DT_F32)
         RFX_LAUNCH(rglru_scan_kernel<float>, grid, 128, 0, s, u, gates, r_bias, i_bias, lam, decay_scale, proj,
                    ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off, seq_slot, seq_row0,

@@ -618,8 +618,10 @@ def attention_prefill(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_
 
 
 def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, seq_start, seq_new,
-                         seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None) -> torch.Tensor:
-    """The tcgen05/TMEM form of `attention_prefill`, for head sizes 64 and 128."""
+                         seq_row0, max_new: int, nq, nkv, head_dim, window, scale, sink=None,
+                         slopes=None) -> torch.Tensor:
+    """The tcgen05/TMEM form of `attention_prefill`, for head sizes 64 and 128
+    (with `slopes` the scale must be positive)."""
     _chk(q, "q", torch.bfloat16)
     if head_dim not in (64, 128):
         raise InvalidInput(f"attention_prefill_tc takes head_dim 64 or 128, got {head_dim}")
@@ -632,7 +634,8 @@ def attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, seq_slot, s
         _chk(seq_slot, "seq_slot", torch.int32), _chk(seq_start, "seq_start", torch.int32),
         _chk(seq_new, "seq_new", torch.int32), _chk(seq_row0, "seq_row0", torch.int32), out.data_ptr(),
         seq_slot.numel(), int(max_new), q.shape[0], nq, nkv, head_dim, int(window or 0), float(scale),
-        _chk(sink, "sink", torch.float32), device_error_word(q.device).data_ptr(), _stream())
+        _chk(sink, "sink", torch.float32), _chk(slopes, "slopes", torch.float32),
+        device_error_word(q.device).data_ptr(), _stream())
     native.check(st, f"attention_prefill_tc (head_dim={head_dim})")
     return out
 
@@ -643,18 +646,17 @@ def attention(q, k_pages, v_pages, page_table, page_size, batch, nq, nkv, head_d
     values; picks the kernel for the dtype and the kind of step.  `sink`: one
     float32 per query head whose exponential joins the softmax's denominator.
     `slopes`: one float32 per query head; slope * (query position - key
-    position) is taken off every score (the tcgen05 prefill kernel has no such
-    term: with slopes the mma.sync one takes its head sizes too)."""
+    position) is taken off every score."""
     fast = q.dtype == torch.bfloat16 and head_dim % 16 == 0 and head_dim <= 256
     if fast and batch.is_decode:
         pages = -(-min(batch.max_context, window or batch.max_context) // page_size) + (1 if window else 0)
         return attention_decode(q, k_pages, v_pages, page_table, page_size, batch.row_pos,
                                 batch.row_slot, nq, nkv, head_dim, window, scale,
                                 n_splits=decode_splits(q.shape[0], nq, nkv, pages), sink=sink, slopes=slopes)
-    if fast and nq // nkv <= 128 and head_dim in (64, 128) and slopes is None:
+    if fast and nq // nkv <= 128 and head_dim in (64, 128) and (slopes is None or scale > 0):
         return attention_prefill_tc(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                     batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
-                                    nkv, head_dim, window, scale, sink)
+                                    nkv, head_dim, window, scale, sink, slopes)
     if fast and nq // nkv <= 128:
         return attention_prefill(q, k_pages, v_pages, page_table, page_size, batch.seq_slot,
                                  batch.seq_start, batch.seq_new, batch.seq_row0, batch.max_new, nq,
@@ -1089,15 +1091,22 @@ def conv_qkv_post(proj: torch.Tensor, bias: Optional[torch.Tensor], weight: torc
     return q
 
 
+RGLRU_CHUNK_MIN_ROWS = _env_int("REFLEX_B200_RGLRU_CHUNK_MIN_ROWS", 16, 1, 1 << 30)
+
+
 def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.Tensor, decay_scale: float,
                proj: torch.Tensor, y_off: int, y_bias, state: torch.Tensor, state_off: int, batch, blocks: int,
-               out_dtype: torch.dtype) -> torch.Tensor:
+               out_dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
     """The gated linear recurrence over the step's rows, sequence by sequence
     (csrc/rglru.cu): `u` float32 [R, W] its input, `gates` float32 [R, blocks,
     2 W / blocks] the two gates' pre-activations, `proj` holds the other
     branch's pre-activation at column `y_off`; the running S is `state[slot,
-    state_off : state_off + W]`.  Returns S * gelu_tanh(y), [R, W]."""
+    state_off : state_off + W]`.  Returns S * gelu_tanh(y), [R, W].  `max_rows`:
+    the most rows any sequence brings; from `RGLRU_CHUNK_MIN_ROWS` on the kernel
+    that folds 64 rows at a time runs, else the row-by-row walk: the same
+    function, rounded differently."""
     R, W = u.shape
+    chunked = max_rows is not None and max_rows >= RGLRU_CHUNK_MIN_ROWS
     out = _new((R, W), out_dtype, u.device)
     st = native.lib().rfx_rglru_scan(
         _chk(u, "u", torch.float32), _chk(gates, "gates", torch.float32), _chk(r_bias, "r_bias", torch.float32),
@@ -1105,7 +1114,8 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.
         _chk(proj, "proj", torch.float32), proj.shape[1], int(y_off), _chk(y_bias, "y_bias", torch.float32),
         _chk(state, "state", torch.float32), state.stride(0), int(state_off),
         _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
-        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), W, int(blocks), _stream())
+        batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), W, int(blocks), 1 if chunked else 0,
+        _stream())
     native.check(st, f"rglru_scan (width={W}, blocks={blocks})")
     return out
 

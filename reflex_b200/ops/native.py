@@ -53,7 +53,7 @@ _SIGNATURES = {
                               c_float, c_void_p, c_void_p, c_void_p],
     "rfx_attention_prefill_tc": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                 c_int, c_int, c_float, c_void_p, c_void_p, c_void_p],
+                                 c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
     "rfx_layernorm": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_void_p,
                       c_int, c_int, c_void_p],
     "rfx_bigram_add": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -91,7 +91,7 @@ _SIGNATURES = {
                               c_int, c_int, c_void_p],
     "rfx_rglru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                       c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_void_p],
     "rfx_branch_norm_mean": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                              c_void_p],
     "rfx_glu_clamped": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],

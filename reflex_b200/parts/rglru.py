@@ -91,7 +91,8 @@ class GatedLinearRecurrence:
         gates = ops.heads_linear(u, self.gates)  # [rows, blocks * 2K], 32-bit
         ops.prof_mark("rglru_gates")
         act = ops.rglru_scan(u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay_scale, proj, 0,
-                             self.y_bias, state, (self.taps - 1) * Wr, batch, self.blocks, self.dtype)
+                             self.y_bias, state, (self.taps - 1) * Wr, batch, self.blocks, self.dtype,
+                             max_rows=batch.max_new)
         ops.prof_mark("rglru_scan")
         out = ops.linear(act, self.o, out_dtype=torch.float32)
         ops.prof_mark("o_proj")

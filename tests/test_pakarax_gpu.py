@@ -148,7 +148,8 @@ SLOPE_CASES = [  # nq, nkv, d, [(start, n_new)], window
 ]
 
 
-@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "decode_bf16", "dispatch_bf16"])
+@pytest.mark.parametrize("kernel", ["plain_f32", "plain_bf16", "prefill_bf16", "prefill_tc_bf16", "decode_bf16",
+                                    "dispatch_bf16"])
 @pytest.mark.parametrize("nq,nkv,d,seqs,window", SLOPE_CASES)
 def test_attention_with_distance_slopes_and_a_sink_in_every_kernel(kernel, nq, nkv, d, seqs, window):
     """slope * (i - j) comes off every score, beside a sink.  The first key of
@@ -157,6 +158,8 @@ def test_attention_with_distance_slopes_and_a_sink_in_every_kernel(kernel, nq, n
     still finds it hundreds of tokens later."""
     if not kernel.startswith("plain") and d % 16:
         pytest.skip("multiples of 16")
+    if kernel == "prefill_tc_bf16" and d not in (64, 128):
+        pytest.skip("head sizes 64 and 128")
     g = torch.Generator().manual_seed(nq + d)
     dtype = torch.float32 if kernel == "plain_f32" else torch.bfloat16
     if kernel == "decode_bf16":
@@ -199,21 +202,24 @@ def test_attention_with_distance_slopes_and_a_sink_in_every_kernel(kernel, nq, n
             b.max_context = max(a + n for a, n in seqs)
             outs.append(ops().attention(qd, kd, vd, td, 64, b, nq, nkv, d, window, scale, sink=sd, slopes=ld))
         else:
-            outs.append(ops().attention_prefill(qd, kd, vd, td, 64, i32(slots), i32([a for a, _ in seqs]),
-                                                i32([b for _, b in seqs]), i32(row0), max(b for _, b in seqs),
-                                                nq, nkv, d, window, scale, sink=sd, slopes=ld))
+            fn = ops().attention_prefill_tc if kernel == "prefill_tc_bf16" else ops().attention_prefill
+            outs.append(fn(qd, kd, vd, td, 64, i32(slots), i32([a for a, _ in seqs]), i32([b for _, b in seqs]),
+                           i32(row0), max(b for _, b in seqs), nq, nkv, d, window, scale, sink=sd, slopes=ld))
     ops().check_device_errors(DEV)
     for out in outs:
         assert not bool(torch.isnan(out.float()).any())
         assert relerr(out.reshape(R, nq, d), ref) < (3e-6 if dtype == torch.float32 else 8e-3)
 
 
+@pytest.mark.parametrize("chunked", [False, True])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W,blocks", [(48, 3), (10, 1), (130, 5), (256, 2)])
-def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype):
+def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype, chunked):
     """The recurrence over sequences cut into unequal steps; S goes on from step
     to step in the state vector, beside the convolution's floats, which it
-    leaves alone; gates that swing from shut to open, decays from 2^-8 to 1."""
+    leaves alone; gates that swing from shut to open, decays from 2^-8 to 1.
+    Both kernels: the row-by-row walk and the one that folds 64 rows at a time
+    (whole tiles, partial ones, single rows)."""
     g = torch.Generator().manual_seed(W)
     K = W // blocks
     lens, slots = {0: 70, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
@@ -232,7 +238,7 @@ def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype):
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [fed[s] for s in ids])
         cat = lambda d: torch.cat([d[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV)  # noqa: E731
         out = ops().rglru_scan(cat(u), cat(gates), rb.to(DEV), ib.to(DEV), lam.to(DEV), 8.0, cat(proj), y_off,
-                               yb.to(DEV), state, off, b, blocks, out_dtype)
+                               yb.to(DEV), state, off, b, blocks, out_dtype, max_rows=10 ** 6 if chunked else None)
         for j, s in enumerate(ids):
             got[s].append(out[b.row0[j]:b.row0[j + 1]].float().cpu())
             fed[s] += cuts[s]
@@ -250,7 +256,8 @@ def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype):
         assert relerr(torch.cat(got[s]), np.stack(ref)) < (5e-6 if out_dtype == torch.float32 else 8e-3), s
 
 
-def test_a_slow_decay_keeps_its_digits():
+@pytest.mark.parametrize("chunked", [False, True])
+def test_a_slow_decay_keeps_its_digits(chunked):
     """a within 1e-6 of one: sqrt(1 - a^2) must not be lost to rounding, and S
     builds up over a thousand steps as the closed form says."""
     W, n = 4, 1200
@@ -262,7 +269,7 @@ def test_a_slow_decay_keeps_its_digits():
     state = torch.zeros(2, W, device=DEV)
     b = FakeBatch([[0] * n], [1], [0])
     out = ops().rglru_scan(u.to(DEV), gates.to(DEV), None, None, lam.to(DEV), 8.0, proj.to(DEV), 0, None, state, 0,
-                           b, 1, torch.float32).cpu().double().numpy()
+                           b, 1, torch.float32, max_rows=n if chunked else None).cpu().double().numpy()
     la = -8.0 * pp.softplus(np.array(-16.0))
     a = np.exp(la)
     want = 30.0 * np.sqrt(-np.expm1(2 * la)) * (1 - a ** np.arange(1, n + 1)) / (1 - a)
