@@ -16,14 +16,15 @@
 // Two kernels.  A few rows a sequence (decode): a thread owns one channel of
 // one sequence and walks the step's rows in order.  Many rows (prompts): the
 // recurrence is linear, S_t = a_t S_(t-1) + b_t, so a stretch of rows folds into
-// one pair (P, B) with S_end = P S_begin + B; a block owns 16 channels of a
-// sequence and takes 64 rows at a time, 16 groups of threads with 4 rows each:
+// one pair (P, B) with S_end = P S_begin + B; a block owns 8 channels of a
+// sequence and takes 128 rows at a time, 32 groups of threads with 4 rows each:
 // every thread loads its rows, does all the gates' arithmetic and folds its 4
 // rows (keeping each row's own pair), the groups' pairs meet in shared memory,
 // every thread folds the groups before it onto the carried S, and then writes
-// its rows' outputs.  The loads and the exponentials of 64 rows run side by
-// side; only 16 multiply-adds a tile are in sequence.  Both kernels compute the
-// same function, rounded differently.
+// its rows' outputs.  The loads and the exponentials of 128 rows run side by
+// side, the next tile's loads are already under way, and only 32 multiply-adds
+// a tile are in sequence.  Both kernels compute the same function, rounded
+// differently.
 #include "common.cuh"
 
 namespace {
@@ -73,7 +74,11 @@ rglru_scan_kernel(const float* __restrict__ u, const float* __restrict__ gates,
     *sp = S;
 }
 
-constexpr int CH_CHANNELS = 16, CH_GROUPS = 16, CH_ROWS = 4;  // 64 rows a tile
+constexpr int CH_CHANNELS = 8, CH_GROUPS = 32, CH_ROWS = 4;  // 128 rows a tile
+
+struct RowIn {
+    float u, r, i, y;
+};
 
 template <typename TO>
 __global__ void __launch_bounds__(CH_CHANNELS * CH_GROUPS)
@@ -100,21 +105,39 @@ rglru_chunk_kernel(const float* __restrict__ u, const float* __restrict__ gates,
     const float rate = -decay_scale * softplus_f(lam[cc]);
     if (grp == 0) carry[0][cl] = *sp;
     int cur = 0;
+    // a tile's loads are issued one tile ahead, so that they travel during the tile before
+    auto fetch = [&](int tile, RowIn (&in)[CH_ROWS]) {
+#pragma unroll
+        for (int j = 0; j < CH_ROWS; ++j) {
+            const int t = tile + grp * CH_ROWS + j;
+            if (t < n) {
+                const size_t row = (size_t)(row0 + t);
+                in[j].u = u[row * W + cc];
+                in[j].r = gates[row * 2 * W + g_r];
+                in[j].i = gates[row * 2 * W + g_i];
+                in[j].y = proj[row * ld + y_off + cc];
+            }
+        }
+    };
+    RowIn ahead[CH_ROWS];
+    fetch(0, ahead);
     for (int tile = 0; tile < n; tile += CH_GROUPS * CH_ROWS) {
+        RowIn in[CH_ROWS];
+#pragma unroll
+        for (int j = 0; j < CH_ROWS; ++j) in[j] = ahead[j];
+        if (tile + CH_GROUPS * CH_ROWS < n) fetch(tile + CH_GROUPS * CH_ROWS, ahead);
         float P[CH_ROWS], B[CH_ROWS], Y[CH_ROWS];
         float p = 1.0f, acc = 0.0f;
 #pragma unroll
         for (int j = 0; j < CH_ROWS; ++j) {
             const int t = tile + grp * CH_ROWS + j;
             if (t < n) {
-                const size_t row = (size_t)(row0 + t);
-                const float uv = u[row * W + cc];
-                const float r = sigmoid_f(gates[row * 2 * W + g_r] + rb);
-                const float i = sigmoid_f(gates[row * 2 * W + g_i] + ib);
-                Y[j] = gelu_tanh_f(proj[row * ld + y_off + cc] + yb);
+                const float r = sigmoid_f(in[j].r + rb);
+                const float i = sigmoid_f(in[j].i + ib);
+                Y[j] = gelu_tanh_f(in[j].y + yb);
                 const float log_a = rate * r;
                 const float a = expf(log_a);
-                acc = fmaf(a, acc, sqrtf(-expm1f(2.0f * log_a)) * (i * uv));
+                acc = fmaf(a, acc, sqrtf(-expm1f(2.0f * log_a)) * (i * in[j].u));
                 p *= a;
             } else {
                 Y[j] = 0.0f;

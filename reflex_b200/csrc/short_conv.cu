@@ -5,7 +5,10 @@
 // the current token.  The last taps - 1 inputs of every sequence are its state
 // ([slot][taps - 1][channels], 32-bit, oldest first, zero when a slot is
 // taken), so a step continues where the one before ended, however the tokens
-// were cut.  All arithmetic is 32-bit; the taps are summed oldest first.
+// were cut.  All arithmetic is 32-bit; the taps are summed oldest first.  The
+// filters come transposed, [taps][channels], so that neighbouring channels'
+// taps are neighbours in memory.  Where every size is a multiple of four a
+// thread takes four neighbouring channels with 16-byte accesses.
 //
 //  * rfx_short_conv: the convolution of a block of columns of `proj`, 32-bit out.
 //  * rfx_conv_qkv_post: the convolution of the stacked q | k | v columns, then
@@ -31,11 +34,17 @@ using namespace rfx;
 
 constexpr int MAX_TAPS = 16;
 
-// rows of this step that precede row r in its sequence, up to `cap`
+// rows of this step that precede row r in its sequence, up to `cap`; the slots of
+// the rows before are loaded side by side, not one after the other's answer
 __device__ __forceinline__ int rows_before(const int* __restrict__ row_slot, int r, int cap) {
     const int slot = row_slot[r];
+    bool same[MAX_TAPS - 1];
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j) same[j] = (j < cap && r - j - 1 >= 0) ? row_slot[r - j - 1] == slot : false;
     int t = 0;
-    while (t < cap && r - t - 1 >= 0 && row_slot[r - t - 1] == slot) ++t;
+#pragma unroll
+    for (int j = 0; j < MAX_TAPS - 1; ++j)
+        if (t == j && same[j]) t = j + 1;
     return t;
 }
 
@@ -52,7 +61,33 @@ __device__ __forceinline__ float conv_at(const float* __restrict__ proj, int ld,
         float u;
         if (back <= before) u = proj[(size_t)(r - back) * ld + col0 + c] + b;
         else u = state_slot[(size_t)(T + before - back) * C + c];
-        y = fmaf(w[(size_t)c * taps + j], u, y);
+        y = fmaf(w[(size_t)j * C + c], u, y);
+    }
+    return y;
+}
+
+// the same for channels c .. c + 3 (every offset a multiple of four floats)
+__device__ __forceinline__ float4 conv4_at(const float* __restrict__ proj, int ld, int col0, int c,
+                                           const float* __restrict__ bias, const float* __restrict__ w,
+                                           int taps, const float* __restrict__ state_slot, int C, int r,
+                                           int before) {
+    const int T = taps - 1;
+    const float4 b = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (int j = 0; j < taps; ++j) {
+        const int back = T - j;
+        float4 u;
+        if (back <= before) {
+            u = *reinterpret_cast<const float4*>(proj + (size_t)(r - back) * ld + col0 + c);
+            u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+        } else {
+            u = *reinterpret_cast<const float4*>(state_slot + (size_t)(T + before - back) * C + c);
+        }
+        const float4 f = *reinterpret_cast<const float4*>(w + (size_t)j * C + c);
+        y.x = fmaf(f.x, u.x, y.x);
+        y.y = fmaf(f.y, u.y, y.y);
+        y.z = fmaf(f.z, u.z, y.z);
+        y.w = fmaf(f.w, u.w, y.w);
     }
     return y;
 }
@@ -61,14 +96,27 @@ __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* __restrict__ proj, int ld, int col0, const float* __restrict__ bias,
                   const float* __restrict__ w, const float* __restrict__ cbias, int taps,
                   const float* __restrict__ state, size_t slot_stride, const int* __restrict__ row_slot,
-                  float* __restrict__ out, int C) {
+                  float* __restrict__ out, __nv_bfloat16* __restrict__ out_lo, int C, int by4) {
     pdl_prologue();
     const int r = blockIdx.x;
     const int before = rows_before(row_slot, r, taps - 1);
     const float* tail = state ? state + (size_t)row_slot[r] * slot_stride : nullptr;
+    if (by4) {
+        for (int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x); c < C; c += 4 * gridDim.y * blockDim.x) {
+            float4 y = conv4_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before);
+            if (cbias) {
+                const float4 cb = *reinterpret_cast<const float4*>(cbias + c);
+                y.x += cb.x; y.y += cb.y; y.z += cb.z; y.w += cb.w;
+            }
+            store4(out + (size_t)r * C + c, y);
+            if (out_lo) store4(out_lo + (size_t)r * C + c, y);
+        }
+        return;
+    }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
-        const float y = conv_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before);
-        out[(size_t)r * C + c] = y + (cbias ? cbias[c] : 0.0f);
+        const float y = conv_at(proj, ld, col0, c, bias, w, taps, tail, C, r, before) + (cbias ? cbias[c] : 0.0f);
+        out[(size_t)r * C + c] = y;
+        if (out_lo) out_lo[(size_t)r * C + c] = __float2bfloat16_rn(y);
     }
 }
 
@@ -79,7 +127,7 @@ conv_qkv_post_kernel(const float* __restrict__ proj, int ld, const float* __rest
                      size_t slot_stride, const int* __restrict__ row_pos, const int* __restrict__ row_slot,
                      TO* __restrict__ q_out, TO* __restrict__ k_pages, TO* __restrict__ v_pages,
                      PagedKV cache, int nq, int nkv, int dim, int vdim, int pad, float temp_coef,
-                     int temp_every, int writes_cache) {
+                     int temp_every, int writes_cache, int by4) {
     pdl_prologue();
     const int r = blockIdx.x;
     const int pos = row_pos[r], slot = row_slot[r];
@@ -89,6 +137,32 @@ conv_qkv_post_kernel(const float* __restrict__ proj, int ld, const float* __rest
     float temp = 1.0f;
     if (temp_coef != 0.0f) temp = fmaf(temp_coef, logf((float)((pos + 1) / temp_every + 1)), 1.0f);
     const int n_out = (nq + (writes_cache ? 2 * nkv : 0)) * pad;
+    if (by4) {
+        // four neighbouring elements of one head a thread (pad, dim and vdim are multiples of four)
+        const size_t kv_row = writes_cache ? kv_offset(cache, slot, pos, 0) : 0;
+        const size_t kv_head = (size_t)cache.page_size * pad;  // from one kv head's tile to the next
+        for (int o = 4 * (blockIdx.y * blockDim.x + threadIdx.x); o < n_out; o += 4 * gridDim.y * blockDim.x) {
+            const int head = o / pad, e = o % pad;
+            float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (head < nq) {
+                if (e < dim) {
+                    y = conv4_at(proj, ld, 0, head * dim + e, bias, w, taps, tail, C, r, before);
+                    y.x *= temp; y.y *= temp; y.z *= temp; y.w *= temp;
+                }
+                store4(q_out + ((size_t)r * nq + head) * pad + e, y);
+            } else if (head < nq + nkv) {
+                const int kvh = head - nq;
+                if (e < dim) y = conv4_at(proj, ld, 0, nq * dim + kvh * dim + e, bias, w, taps, tail, C, r, before);
+                store4(k_pages + kv_row + kvh * kv_head + e, y);
+            } else {
+                const int kvh = head - nq - nkv;
+                if (e < vdim)
+                    y = conv4_at(proj, ld, 0, (nq + nkv) * dim + kvh * vdim + e, bias, w, taps, tail, C, r, before);
+                store4(v_pages + kv_row + kvh * kv_head + e, y);
+            }
+        }
+        return;
+    }
     for (int o = blockIdx.y * blockDim.x + threadIdx.x; o < n_out; o += gridDim.y * blockDim.x) {
         const int head = o / pad, e = o % pad;
         if (head < nq) {
@@ -138,16 +212,23 @@ int chunks(int n, int threads) {
     return g < 1 ? 1 : (g > 64 ? 64 : g);
 }
 
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 }  // namespace
 
+// `w`: the filters transposed, [taps][C].  `out_lo` (may be null): the result once
+// more, rounded to bfloat16 (the input of a tensor-core product).
 extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* bias, const float* w,
                               const float* cbias, int taps, const float* state, long long slot_stride,
-                              const int* row_slot, float* out, int R, int C, void* stream) {
+                              const int* row_slot, float* out, void* out_lo, int R, int C, void* stream) {
     if (R <= 0 || C <= 0) return 0;
     if (taps < 1 || taps > MAX_TAPS || (taps > 1 && !state)) return RFX_ERR_BAD_ARG;
-    dim3 grid(R, chunks(C, 256));
+    const int by4 = C % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && slot_stride % 4 == 0 && aligned16(proj) &&
+                    aligned16(bias) && aligned16(w) && aligned16(cbias) && aligned16(state) && aligned16(out) &&
+                    ((reinterpret_cast<uintptr_t>(out_lo) & 7) == 0);
+    dim3 grid(R, chunks(by4 ? C / 4 : C, 256));
     RFX_LAUNCH(short_conv_kernel, grid, 256, 0, (cudaStream_t)stream, proj, ld, col0, bias, w, cbias, taps,
-               state, (size_t)slot_stride, row_slot, out, C);
+               state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4);
     return 0;
 }
 
@@ -162,17 +243,20 @@ extern "C" int rfx_conv_qkv_post(const float* proj, int ld, const float* bias, c
         nq % nkv != 0 || (temp_coef != 0.0f && temp_every <= 0))
         return RFX_ERR_BAD_ARG;
     PagedKV cache{page_table, max_pages, page_size, nkv, pad};
-    dim3 grid(R, chunks((nq + 2 * nkv) * pad, 256));
+    const int by4 = dim % 4 == 0 && vdim % 4 == 0 && pad % 4 == 0 && ld % 4 == 0 && slot_stride % 4 == 0 &&
+                    aligned16(proj) && aligned16(bias) && aligned16(w) && aligned16(state) && aligned16(q_out) &&
+                    aligned16(k_pages) && aligned16(v_pages);
+    dim3 grid(R, chunks((nq + 2 * nkv) * pad / (by4 ? 4 : 1), 256));
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dt == RFX_DT_F32)
         RFX_LAUNCH(conv_qkv_post_kernel<float>, grid, 256, 0, s, proj, ld, bias, w, taps, state,
                    (size_t)slot_stride, row_pos, row_slot, (float*)q_out, (float*)k_pages, (float*)v_pages,
-                   cache, nq, nkv, dim, vdim, pad, temp_coef, temp_every, writes_cache);
+                   cache, nq, nkv, dim, vdim, pad, temp_coef, temp_every, writes_cache, by4);
     else if (out_dt == RFX_DT_BF16)
         RFX_LAUNCH(conv_qkv_post_kernel<__nv_bfloat16>, grid, 256, 0, s, proj, ld, bias, w, taps, state,
                    (size_t)slot_stride, row_pos, row_slot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages,
                    (__nv_bfloat16*)v_pages, cache, nq, nkv, dim, vdim, pad, temp_coef, temp_every,
-                   writes_cache);
+                   writes_cache, by4);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

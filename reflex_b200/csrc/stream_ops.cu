@@ -59,6 +59,48 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
     }
 }
 
+// bfloat16, I a multiple of 8, 16-byte aligned rows: eight outputs a thread and step
+__global__ void __launch_bounds__(256)
+glu_clamped_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int R, int I,
+                          int alternating, float alpha, float limit) {
+    pdl_prologue();
+    const size_t n8 = (size_t)R * (I / 8);
+    const unsigned i8 = (unsigned)(I / 8);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 *pa, *pb;
+        if (alternating) {  // output pack i comes from input elements [16 i, 16 i + 16)
+            pa = reinterpret_cast<const uint4*>(gu + 16 * i);
+            pb = pa + 1;
+        } else {
+            const size_t r = i / i8, c = (i - r * i8) * 8;
+            pa = reinterpret_cast<const uint4*>(gu + r * 2 * I + c);
+            pb = reinterpret_cast<const uint4*>(gu + r * 2 * I + I + c);
+        }
+        const uint4 a = *pa, b = *pb;
+        const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 o;
+        __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+        if (alternating) {  // a = g0 u0 g1 u1 g2 u2 g3 u3, b = g4 u4 ...
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float2 p0 = __bfloat1622float2(ha[2 * j]), p1 = __bfloat1622float2(ha[2 * j + 1]);
+                const float2 q0 = __bfloat1622float2(hb[2 * j]), q1 = __bfloat1622float2(hb[2 * j + 1]);
+                ho[j] = __floats2bfloat162_rn(glu_clamped(p0.x, p0.y, alpha, limit), glu_clamped(p1.x, p1.y, alpha, limit));
+                ho[2 + j] = __floats2bfloat162_rn(glu_clamped(q0.x, q0.y, alpha, limit),
+                                                  glu_clamped(q1.x, q1.y, alpha, limit));
+            }
+        } else {  // a = eight gates, b = their ups
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 g = __bfloat1622float2(ha[j]), up = __bfloat1622float2(hb[j]);
+                ho[j] = __floats2bfloat162_rn(glu_clamped(g.x, up.x, alpha, limit), glu_clamped(g.y, up.y, alpha, limit));
+            }
+        }
+        *reinterpret_cast<uint4*>(out + 8 * i) = o;
+    }
+}
+
 template <typename T>
 __global__ void row_gate_add_kernel(float* __restrict__ y, const T* __restrict__ s, const float* __restrict__ z,
                                     int ldz, int col, int H) {
@@ -114,6 +156,10 @@ extern "C" int rfx_glu_clamped(const void* gate_up, void* out, int dt, int R, in
     if (dt == RFX_DT_F32)
         RFX_LAUNCH(glu_clamped_kernel<float>, blocks, 256, 0, s, (const float*)gate_up, (float*)out, R, I,
                    alternating, alpha, limit);
+    else if (dt == RFX_DT_BF16 && I % 8 == 0 &&
+             ((reinterpret_cast<uintptr_t>(gate_up) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+        RFX_LAUNCH(glu_clamped_bf16x8_kernel, blocks_for((size_t)R * I / 8), 256, 0, s,
+                   (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, R, I, alternating, alpha, limit);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(glu_clamped_kernel<__nv_bfloat16>, blocks, 256, 0, s, (const __nv_bfloat16*)gate_up,
                    (__nv_bfloat16*)out, R, I, alternating, alpha, limit);

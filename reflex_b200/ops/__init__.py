@@ -740,19 +740,33 @@ def latent_post(proj: torch.Tensor, q_weight: torch.Tensor, kv_weight: torch.Ten
 HEADS_LINEAR_MAX_ROWS = _env_int("REFLEX_B200_HEADS_LINEAR_MAX_ROWS", 64, 0, 1 << 30)
 
 
-def heads_linear(x: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+def heads_linear(x: torch.Tensor, weight: torch.Tensor, scale: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """y[r, b, :] = x[r, b, :] @ weight[b].T for every head b: x [R, heads * K],
     weight [heads, N, K], y [R, heads * N]; with `scale` (float32 [R, heads])
     y[r, b, :] is multiplied by scale[r, b].  float32 and a few bfloat16 rows:
     this library's kernel (32-bit accumulation in index order); more bfloat16
-    rows: the library's batched product, then the scaling kernel."""
+    rows: the library's batched product, then the scaling kernel.  `out_dtype`
+    float32 with bfloat16 operands (many rows only): the batched product's
+    32-bit sums come out unrounded."""
     heads, N, K = weight.shape
     R = x.shape[0]
     if x.shape[1] != heads * K or x.dtype != weight.dtype:
         raise InvalidInput("heads_linear: x must be [rows, heads * K] in the weight's dtype")
     _chk(x, "x")
     _chk(weight, "weight")
-    y = _new((R, heads * N), x.dtype, x.device)
+    wide = out_dtype == torch.float32 and x.dtype == torch.bfloat16
+    if wide and R <= HEADS_LINEAR_MAX_ROWS:
+        raise InvalidInput("heads_linear: 32-bit results of bfloat16 operands need more rows than its own kernel takes")
+    y = _new((R, heads * N), torch.float32 if wide else x.dtype, x.device)
+    if wide:
+        torch.bmm(x.view(R, heads, K).transpose(0, 1), weight.transpose(1, 2), out_dtype=torch.float32,
+                  out=y.view(R, heads, N).transpose(0, 1))
+        if scale is not None:
+            st = native.lib().rfx_scale_heads(y.data_ptr(), dt_code(y.dtype), _chk(scale, "scale", torch.float32),
+                                              y.numel(), N, _stream())
+            native.check(st, "scale_heads")
+        return y
     if x.dtype == torch.bfloat16 and R > HEADS_LINEAR_MAX_ROWS:
         torch.bmm(x.view(R, heads, K).transpose(0, 1), weight.transpose(1, 2),
                   out=y.view(R, heads, N).transpose(0, 1))
@@ -1034,24 +1048,29 @@ def branch_norm_mean(a: torch.Tensor, a_bias: Optional[torch.Tensor], wa: torch.
 
 
 # ------------------------------------------- short convolutions, gated recurrence
-def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], weight: torch.Tensor,
-               conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch) -> torch.Tensor:
+def short_conv(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], filters_t: torch.Tensor,
+               conv_bias: Optional[torch.Tensor], state: Optional[torch.Tensor], batch, also_bf16: bool = False):
     """A causal convolution over time of columns [col0, col0 + channels) of
-    `proj` (float32 [R, ld]) plus `bias`, one filter a channel (`weight`
-    float32 [channels, taps], the last tap on the current token) plus
-    `conv_bias`; what lies before a step's rows comes from `state` ([slots, n]
-    float32, whose first (taps - 1) * channels floats are the sequence's last
-    inputs, oldest first).  float32 [R, channels]."""
+    `proj` (float32 [R, ld]) plus `bias`, one filter a channel (`filters_t`
+    float32 [taps, channels], transposed; the last tap on the current token)
+    plus `conv_bias`; what lies before a step's rows comes from `state` ([slots,
+    n] float32, whose first (taps - 1) * channels floats are the sequence's last
+    inputs, oldest first).  float32 [R, channels]; with `also_bf16` a pair, the
+    second the same values rounded to bfloat16."""
     R = proj.shape[0]
-    taps = weight.shape[1]
+    taps = filters_t.shape[0]
+    if filters_t.shape[1] != channels:
+        raise InvalidInput("short_conv: the filters must be [taps, channels]")
     out = _new((R, channels), torch.float32, proj.device)
+    lo = _new((R, channels), torch.bfloat16, proj.device) if also_bf16 else None
     st = native.lib().rfx_short_conv(
         _chk(proj, "proj", torch.float32), proj.shape[1], int(col0), _chk(bias, "bias", torch.float32),
-        _chk(weight, "weight", torch.float32), _chk(conv_bias, "conv_bias", torch.float32), taps,
+        _chk(filters_t, "filters_t", torch.float32), _chk(conv_bias, "conv_bias", torch.float32), taps,
         _chk(state, "state", torch.float32), state.stride(0) if state is not None else 0,
-        _chk(batch.row_slot, "row_slot", torch.int32), out.data_ptr(), R, channels, _stream())
+        _chk(batch.row_slot, "row_slot", torch.int32), out.data_ptr(), lo.data_ptr() if lo is not None else 0,
+        R, channels, _stream())
     native.check(st, f"short_conv (taps={taps})")
-    return out
+    return (out, lo) if also_bf16 else out
 
 
 def conv_state_update(proj: torch.Tensor, col0: int, channels: int, bias: Optional[torch.Tensor], taps: int,
@@ -1067,21 +1086,23 @@ def conv_state_update(proj: torch.Tensor, col0: int, channels: int, bias: Option
     native.check(st, "conv_state_update")
 
 
-def conv_qkv_post(proj: torch.Tensor, bias: Optional[torch.Tensor], weight: torch.Tensor,
+def conv_qkv_post(proj: torch.Tensor, bias: Optional[torch.Tensor], filters_t: torch.Tensor,
                   state: Optional[torch.Tensor], batch, k_pages, v_pages, page_table, page_size: int, nq: int,
                   nkv: int, dim: int, vdim: int, pad: int, temp_coef: float, temp_every: int, writes_cache: bool,
                   out_dtype: torch.dtype) -> torch.Tensor:
     """The stacked q | k | v columns of `proj` (float32) plus `bias` through
-    their short convolutions (`weight` float32 [channels, taps]); q times the
+    their short convolutions (`filters_t` float32 [taps, channels]); q times the
     temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p, out as
     [R, nq * pad]; k and v into the cache at the rows' positions, heads `pad`
     wide (zeros beyond `dim` and `vdim`)."""
     R = proj.shape[0]
-    taps = weight.shape[1]
+    taps = filters_t.shape[0]
+    if filters_t.shape[1] != nq * dim + nkv * (dim + vdim):
+        raise InvalidInput("conv_qkv_post: the filters must be [taps, channels of q, k and v]")
     q = _new((R, nq * pad), out_dtype, proj.device)
     st = native.lib().rfx_conv_qkv_post(
         _chk(proj, "proj", torch.float32), proj.shape[1], _chk(bias, "bias", torch.float32),
-        _chk(weight, "weight", torch.float32), taps, _chk(state, "state", torch.float32),
+        _chk(filters_t, "filters_t", torch.float32), taps, _chk(state, "state", torch.float32),
         state.stride(0) if state is not None else 0, _chk(batch.row_pos, "row_pos", torch.int32),
         _chk(batch.row_slot, "row_slot", torch.int32), q.data_ptr(), _chk(k_pages, "k_pages", out_dtype),
         _chk(v_pages, "v_pages", out_dtype), dt_code(out_dtype), _chk(page_table, "page_table", torch.int32),
@@ -1103,7 +1124,7 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.
     branch's pre-activation at column `y_off`; the running S is `state[slot,
     state_off : state_off + W]`.  Returns S * gelu_tanh(y), [R, W].  `max_rows`:
     the most rows any sequence brings; from `RGLRU_CHUNK_MIN_ROWS` on the kernel
-    that folds 64 rows at a time runs, else the row-by-row walk: the same
+    that folds 128 rows at a time runs, else the row-by-row walk: the same
     function, rounded differently."""
     R, W = u.shape
     chunked = max_rows is not None and max_rows >= RGLRU_CHUNK_MIN_ROWS

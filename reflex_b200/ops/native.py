@@ -83,7 +83,7 @@ _SIGNATURES = {
     "rfx_moe_activation": [c_void_p, c_int, c_longlong, c_int, c_void_p],
     "rfx_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_short_conv": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_longlong,
-                       c_void_p, c_void_p, c_int, c_int, c_void_p],
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "rfx_conv_qkv_post": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p,
                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
                           c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],

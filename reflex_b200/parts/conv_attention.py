@@ -91,7 +91,8 @@ class ConvAttention:
             return t.to(device=self.device, dtype=torch.float32).contiguous()
 
         self.qkv = torch.cat([dev(tensors[k]) for k in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
-        self.filters = torch.cat([f32(tensors[k]) for k in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
+        # transposed, [taps, channels]: neighbouring channels' taps side by side
+        self.filters = torch.cat([f32(tensors[k]) for k in ("q_conv", "k_conv", "v_conv")], dim=0).t().contiguous()
         if self.has_bias:
             self.bias = torch.cat([f32(tensors[k]) for k in ("q_bias", "k_bias", "v_bias")]).contiguous()
             self.o_bias = f32(tensors["o_bias"])

@@ -44,7 +44,7 @@ class GatedLinearRecurrence:
         if self.width % self.blocks:
             raise InvalidInput("rglru: width must be a multiple of blocks")
         self.yx = self.y_bias = self.x_bias = self.filters = self.conv_bias = None
-        self.gates = self.gate_a_bias = self.gate_i_bias = self.lam = self.o = None
+        self.gates = self.gates_lo = self.gate_a_bias = self.gate_i_bias = self.lam = self.o = None
 
     @classmethod
     def tensor_specs(cls, spec: MixerSpec) -> Dict[str, TensorInfo]:
@@ -72,9 +72,12 @@ class GatedLinearRecurrence:
 
         self.yx = torch.cat([dev(tensors["y_proj"]), dev(tensors["x_proj"])], dim=0).contiguous()
         self.y_bias, self.x_bias = f32(tensors["y_bias"]), f32(tensors["x_bias"])
-        self.filters, self.conv_bias = f32(tensors["conv"]), f32(tensors["conv_bias"])
+        self.filters, self.conv_bias = f32(tensors["conv"]).t().contiguous(), f32(tensors["conv_bias"])  # [taps, width]
         # a part's two gate matrices stacked, [blocks, 2K, K], 32-bit: one per-part product gives both
         self.gates = torch.cat([f32(tensors["gate_a"]), f32(tensors["gate_i"])], dim=1).contiguous()
+        # the same in bfloat16 for prompts, where the product runs on the tensor cores with 32-bit
+        # sums: exact for weights stored in bfloat16, u rounded once (a convolution's output)
+        self.gates_lo = self.gates.to(torch.bfloat16) if self.dtype == torch.bfloat16 else None
         self.gate_a_bias = f32(tensors["gate_a_bias"]).reshape(-1)
         self.gate_i_bias = f32(tensors["gate_i_bias"]).reshape(-1)
         self.lam = f32(tensors["lam"])
@@ -84,11 +87,16 @@ class GatedLinearRecurrence:
         batch, state, Wr = ctx.batch, ctx.state, self.width
         proj = ops.linear(x, self.yx, out_dtype=torch.float32)  # [rows, y | x]
         ops.prof_mark("qkv_gemm")
+        many = self.gates_lo is not None and x.shape[0] > ops.HEADS_LINEAR_MAX_ROWS
         u = ops.short_conv(proj, Wr, Wr, self.x_bias, self.filters, self.conv_bias,
-                           state if self.taps > 1 else None, batch)
+                           state if self.taps > 1 else None, batch, also_bf16=many)
         ops.conv_state_update(proj, Wr, Wr, self.x_bias, self.taps, state, batch)
         ops.prof_mark("conv_post")
-        gates = ops.heads_linear(u, self.gates)  # [rows, blocks * 2K], 32-bit
+        if many:
+            u, u_lo = u
+            gates = ops.heads_linear(u_lo, self.gates_lo, out_dtype=torch.float32)
+        else:
+            gates = ops.heads_linear(u, self.gates)  # [rows, blocks * 2K], 32-bit
         ops.prof_mark("rglru_gates")
         act = ops.rglru_scan(u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay_scale, proj, 0,
                              self.y_bias, state, (self.taps - 1) * Wr, batch, self.blocks, self.dtype,

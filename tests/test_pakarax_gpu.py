@@ -25,18 +25,18 @@ def f32(a):
 CUTS = ({0: 37, 1: 9, 2: 1}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 15}, {0: 30})  # rows per sequence and step
 
 
+@pytest.mark.parametrize("C,col0,ld", [(20, 3, 30), (24, 4, 32)])  # one channel a thread; four (every size a multiple of 4)
 @pytest.mark.parametrize("taps", [1, 2, 3, 5])
-def test_short_convolution_carried_through_its_state(taps):
+def test_short_convolution_carried_through_its_state(taps, C, col0, ld):
     """Three sequences of unequal lengths in steps of unequal sizes, down to one
     and two rows (fewer than the filter looks back), in slots that are not in
     order: every step goes on from the inputs the steps before left; a slot
     taken again starts from zeros."""
     g = torch.Generator().manual_seed(taps)
-    C, col0, ld = 20, 3, 30
     lens, slots = {0: 70, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
     proj = {s: torch.randn(n, ld, generator=g) for s, n in lens.items()}
     bias, w, cb = torch.randn(C, generator=g), torch.randn(C, taps, generator=g), torch.randn(C, generator=g)
-    extra = 7  # the state vector holds more than the filter's inputs (another part's floats)
+    extra = 8  # the state vector holds more than the filter's inputs (another part's floats)
     state = torch.zeros(8, (taps - 1) * C + extra, device=DEV)
     state[:, (taps - 1) * C:] = 5.0
     fed = {s: 0 for s in lens}
@@ -45,7 +45,9 @@ def test_short_convolution_carried_through_its_state(taps):
         ids = list(cuts)
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [fed[s] for s in ids])
         rows = torch.cat([proj[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV)
-        out = ops().short_conv(rows, col0, C, bias.to(DEV), w.to(DEV), cb.to(DEV), state if taps > 1 else None, b)
+        out, lo = ops().short_conv(rows, col0, C, bias.to(DEV), w.t().contiguous().to(DEV), cb.to(DEV),
+                                   state if taps > 1 else None, b, also_bf16=True)
+        assert torch.equal(lo, out.to(torch.bfloat16))
         ops().conv_state_update(rows, col0, C, bias.to(DEV), taps, state, b)
         for j, s in enumerate(ids):
             got[s].append(out[b.row0[j]:b.row0[j + 1]].cpu())
@@ -62,13 +64,14 @@ def test_short_convolution_carried_through_its_state(taps):
     if taps > 1:
         state[0].zero_()
         b = FakeBatch([[0] * 9], [0], [0])
-        out = ops().short_conv(proj[1].to(DEV), col0, C, bias.to(DEV), w.to(DEV), cb.to(DEV), state, b)
+        out = ops().short_conv(proj[1].to(DEV), col0, C, bias.to(DEV), w.t().contiguous().to(DEV), cb.to(DEV), state, b)
         assert relerr(out, ref(1)) < 3e-6
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,dim,vdim,taps,temp", [(4, 2, 16, 24, 3, (0.3, 7)), (3, 3, 40, 20, 4, (0.5, 64)),
-                                                       (6, 1, 8, 8, 1, None), (2, 1, 64, 64, 2, (1.0, 1))])
+                                                       (6, 1, 8, 8, 1, None), (2, 1, 64, 64, 2, (1.0, 1)),
+                                                       (3, 1, 10, 6, 3, (0.3, 5))])  # the last: one element a thread
 def test_convolved_q_k_v_temperature_and_cache_write(dtype, nq, nkv, dim, vdim, taps, temp):
     """Two steps of two sequences: q out with its temperature, k and v in the
     paged cache at the rows' positions, heads padded with zeros, the second
@@ -92,7 +95,7 @@ def test_convolved_q_k_v_temperature_and_cache_write(dtype, nq, nkv, dim, vdim, 
         ids = list(cuts)
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [starts[s] + fed[s] for s in ids])
         rows = torch.cat([proj[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV)
-        q = ops().conv_qkv_post(rows, bias.to(DEV), w.to(DEV), state if taps > 1 else None, b, k_pages, v_pages,
+        q = ops().conv_qkv_post(rows, bias.to(DEV), w.t().contiguous().to(DEV), state if taps > 1 else None, b, k_pages, v_pages,
                                 table, 64, nq, nkv, dim, vdim, pad, temp[0] if temp else 0.0,
                                 temp[1] if temp else 1, True, dtype)
         ops().conv_state_update(rows, 0, C, bias.to(DEV), taps, state, b)
@@ -218,11 +221,12 @@ def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype, chunke
     """The recurrence over sequences cut into unequal steps; S goes on from step
     to step in the state vector, beside the convolution's floats, which it
     leaves alone; gates that swing from shut to open, decays from 2^-8 to 1.
-    Both kernels: the row-by-row walk and the one that folds 64 rows at a time
+    Both kernels: the row-by-row walk and the one that folds 128 rows at a time
     (whole tiles, partial ones, single rows)."""
     g = torch.Generator().manual_seed(W)
     K = W // blocks
-    lens, slots = {0: 70, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
+    lens, slots = {0: 335, 1: 9, 2: 33}, {0: 3, 1: 0, 2: 6}
+    cuts_list = ({0: 200, 1: 9, 2: 1}, {0: 1, 2: 2}, {2: 1}, {0: 2, 2: 14}, {2: 15}, {0: 132})
     ld, y_off, off = W + 5, 2, 11
     u = {s: torch.randn(n, W, generator=g) for s, n in lens.items()}
     gates = {s: torch.randn(n, 2 * W, generator=g) * 4 for s, n in lens.items()}
@@ -233,7 +237,7 @@ def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype, chunke
     state[:, :off] = 7.0
     fed = {s: 0 for s in lens}
     got = {s: [] for s in lens}
-    for cuts in CUTS:
+    for cuts in cuts_list:
         ids = list(cuts)
         b = FakeBatch([[0] * cuts[s] for s in ids], [slots[s] for s in ids], [fed[s] for s in ids])
         cat = lambda d: torch.cat([d[s][fed[s]:fed[s] + cuts[s]] for s in ids]).to(DEV)  # noqa: E731
@@ -292,9 +296,10 @@ def test_two_branches_normed_and_averaged():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("alternating", [False, True])
-def test_clamped_gated_activation(dtype, alternating):
+@pytest.mark.parametrize("I", [52, 64])  # one output a thread; eight
+def test_clamped_gated_activation(dtype, alternating, I):
     g = torch.Generator().manual_seed(1)
-    R, I, limit = 7, 52, 1.25
+    R, limit = 7, 1.25
     gate, up = (torch.randn(R, I, generator=g) * 3).to(dtype), (torch.randn(R, I, generator=g) * 3).to(dtype)
     gate[0, :4] = torch.tensor([-40.0, 40.0, 1.25, -1.25]).to(dtype)
     gd, ud = gate.double().numpy(), up.double().numpy()
