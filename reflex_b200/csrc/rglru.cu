@@ -37,6 +37,25 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// The convolution before the recurrence keeps its last taps - 1 inputs (columns
+// x_off.. of proj, plus x_bias) beside S, [taps - 1][W] at `tail`, oldest first.
+// That convolution ran in the launch before this one, so this kernel may bring
+// them up to date: place i takes the input at local time n - T + i, one of the
+// step's rows or what the state held n places later (read before it is written:
+// a thread owns its channel and goes through i upwards).
+__device__ __forceinline__ void update_tail(const float* __restrict__ proj, int ld, int x_off,
+                                            const float* __restrict__ x_bias, int taps, float* __restrict__ tail,
+                                            int W, int c, int row0, int n) {
+    const int T = taps - 1;
+    if (T <= 0 || x_off < 0) return;
+    const float b = x_bias ? x_bias[c] : 0.0f;
+    for (int i = 0; i < T; ++i) {
+        const int src = n - T + i;
+        tail[(size_t)i * W + c] = src >= 0 ? proj[(size_t)(row0 + src) * ld + x_off + c] + b
+                                           : tail[(size_t)(n + i) * W + c];
+    }
+}
+
 // gates: [R][blocks][2 * K] (a block's r_pre, then its i_pre); channel c = b * K + k
 template <typename TO>
 __global__ void __launch_bounds__(128)
@@ -45,7 +64,8 @@ rglru_scan_kernel(const float* __restrict__ u, const float* __restrict__ gates,
                   const float* __restrict__ lam, float decay_scale, const float* __restrict__ proj, int ld,
                   int y_off, const float* __restrict__ y_bias, float* __restrict__ state, size_t slot_stride,
                   size_t state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
-                  TO* __restrict__ out, int W, int K) {
+                  TO* __restrict__ out, int W, int K, int x_off, const float* __restrict__ x_bias, int taps,
+                  size_t tail_off) {
     pdl_prologue();
     const int s = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -72,6 +92,7 @@ rglru_scan_kernel(const float* __restrict__ u, const float* __restrict__ gates,
         st<TO>(out, row * W + c, S * yv);
     }
     *sp = S;
+    update_tail(proj, ld, x_off, x_bias, taps, state + (size_t)seq_slot[s] * slot_stride + tail_off, W, c, row0, n);
 }
 
 constexpr int CH_CHANNELS = 8, CH_GROUPS = 32, CH_ROWS = 4;  // 128 rows a tile
@@ -87,7 +108,8 @@ rglru_chunk_kernel(const float* __restrict__ u, const float* __restrict__ gates,
                    const float* __restrict__ lam, float decay_scale, const float* __restrict__ proj, int ld,
                    int y_off, const float* __restrict__ y_bias, float* __restrict__ state, size_t slot_stride,
                    size_t state_off, const int* __restrict__ seq_slot, const int* __restrict__ seq_row0,
-                   TO* __restrict__ out, int W, int K) {
+                   TO* __restrict__ out, int W, int K, int x_off, const float* __restrict__ x_bias, int taps,
+                   size_t tail_off) {
     __shared__ float fold_p[CH_GROUPS][CH_CHANNELS], fold_b[CH_GROUPS][CH_CHANNELS];
     __shared__ float carry[2][CH_CHANNELS];
     pdl_prologue();
@@ -162,17 +184,23 @@ rglru_chunk_kernel(const float* __restrict__ u, const float* __restrict__ gates,
         cur ^= 1;
         __syncthreads();
     }
-    if (live && grp == 0) *sp = carry[cur][cl];
+    if (live && grp == 0) {
+        *sp = carry[cur][cl];
+        update_tail(proj, ld, x_off, x_bias, taps, state + (size_t)seq_slot[s] * slot_stride + tail_off, W, c, row0, n);
+    }
 }
 
 }  // namespace
 
-// `chunked` != 0: the form for many rows a sequence (above)
+// `chunked` != 0: the form for many rows a sequence (above).  `x_off` >= 0 and `taps` > 1:
+// the kernel also brings the preceding convolution's last inputs up to date (columns
+// x_off.. of proj plus x_bias, kept at `tail_off` of a slot's state).
 extern "C" int rfx_rglru_scan(const float* u, const float* gates, const float* r_bias, const float* i_bias,
                               const float* lam, float decay_scale, const float* proj, int ld, int y_off,
                               const float* y_bias, float* state, long long slot_stride, long long state_off,
                               const int* seq_slot, const int* seq_row0, int S, void* out, int out_dt, int W,
-                              int blocks, int chunked, void* stream) {
+                              int blocks, int chunked, int x_off, const float* x_bias, int taps,
+                              long long tail_off, void* stream) {
     if (S <= 0 || W <= 0) return 0;
     if (blocks <= 0 || W % blocks != 0) return RFX_ERR_BAD_ARG;
     dim3 grid(S, (W + 127) / 128);
@@ -184,11 +212,12 @@ extern "C" int rfx_rglru_scan(const float* u, const float* gates, const float* r
         if (out_dt == RFX_DT_F32)
             RFX_LAUNCH(rglru_chunk_kernel<float>, cgrid, CH_CHANNELS * CH_GROUPS, 0, s, u, gates, r_bias, i_bias,
                        lam, decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off,
-                       seq_slot, seq_row0, (float*)out, W, K);
+                       seq_slot, seq_row0, (float*)out, W, K, x_off, x_bias, taps, (size_t)tail_off);
         else if (out_dt == RFX_DT_BF16)
             RFX_LAUNCH(rglru_chunk_kernel<__nv_bfloat16>, cgrid, CH_CHANNELS * CH_GROUPS, 0, s, u, gates, r_bias,
                        i_bias, lam, decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride,
-                       (size_t)state_off, seq_slot, seq_row0, (__nv_bfloat16*)out, W, K);
+                       (size_t)state_off, seq_slot, seq_row0, (__nv_bfloat16*)out, W, K, x_off, x_bias, taps,
+                       (size_t)tail_off);
         else
             return RFX_ERR_BAD_ARG;
         return 0;
@@ -196,11 +225,11 @@ extern "C" int rfx_rglru_scan(const float* u, const float* gates, const float* r
     if (out_dt == RFX_DT_F32)
         RFX_LAUNCH(rglru_scan_kernel<float>, grid, 128, 0, s, u, gates, r_bias, i_bias, lam, decay_scale, proj,
                    ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off, seq_slot, seq_row0,
-                   (float*)out, W, K);
+                   (float*)out, W, K, x_off, x_bias, taps, (size_t)tail_off);
     else if (out_dt == RFX_DT_BF16)
         RFX_LAUNCH(rglru_scan_kernel<__nv_bfloat16>, grid, 128, 0, s, u, gates, r_bias, i_bias, lam,
                    decay_scale, proj, ld, y_off, y_bias, state, (size_t)slot_stride, (size_t)state_off,
-                   seq_slot, seq_row0, (__nv_bfloat16*)out, W, K);
+                   seq_slot, seq_row0, (__nv_bfloat16*)out, W, K, x_off, x_bias, taps, (size_t)tail_off);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

@@ -7,7 +7,7 @@
 //        g' = min(g, limit), u' = clamp(u, -limit, limit),
 //        out = g' * sigmoid(alpha * g') * (u' + 1)
 //    of a row [gates | ups] (or gate_j at 2j and up_j at 2j + 1).
-//  * rfx_row_gate_add: y[r] += sigmoid(z[r]) * s[r], one gate a row.
+//  * rfx_row_gate_add: y[r] += sigmoid(z[r]) * s[r] (+ extra[r]), one gate a row.
 //  * rfx_stream_concat: out[r] = [x[r] (+ delta[r]) | x0[r]], cast, the input of
 //    a product that mixes the stream with the embedding output.
 //  * rfx_logit_finish: z <- z * scale, then cap * tanh(z / cap) when cap > 0.
@@ -103,11 +103,15 @@ glu_clamped_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* _
 
 template <typename T>
 __global__ void row_gate_add_kernel(float* __restrict__ y, const T* __restrict__ s, const float* __restrict__ z,
-                                    int ldz, int col, int H) {
+                                    int ldz, int col, const float* __restrict__ extra, int H) {
     pdl_prologue();
     const size_t r = blockIdx.x;
     const float gate = 1.0f / (1.0f + expf(-z[r * ldz + col]));
-    for (int c = threadIdx.x; c < H; c += blockDim.x) y[r * H + c] = fmaf(gate, ld<T>(s, r * H + c), y[r * H + c]);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = y[r * H + c];
+        if (extra) v += extra[r * H + c];
+        y[r * H + c] = fmaf(gate, ld<T>(s, r * H + c), v);
+    }
 }
 
 template <typename TD, typename TO>
@@ -168,15 +172,15 @@ extern "C" int rfx_glu_clamped(const void* gate_up, void* out, int dt, int R, in
     return 0;
 }
 
-extern "C" int rfx_row_gate_add(float* y, const void* s_rows, int dt, const float* z, int ldz, int col, int R,
-                                int H, void* stream) {
+extern "C" int rfx_row_gate_add(float* y, const void* s_rows, int dt, const float* z, int ldz, int col,
+                                const float* extra, int R, int H, void* stream) {
     if (R <= 0 || H <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(row_gate_add_kernel<float>, R, 256, 0, s, y, (const float*)s_rows, z, ldz, col, H);
+        RFX_LAUNCH(row_gate_add_kernel<float>, R, 256, 0, s, y, (const float*)s_rows, z, ldz, col, extra, H);
     else if (dt == RFX_DT_BF16)
         RFX_LAUNCH(row_gate_add_kernel<__nv_bfloat16>, R, 256, 0, s, y, (const __nv_bfloat16*)s_rows, z, ldz,
-                   col, H);
+                   col, extra, H);
     else
         return RFX_ERR_BAD_ARG;
     return 0;

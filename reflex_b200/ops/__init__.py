@@ -992,11 +992,13 @@ def glu_clamped(gate_up: torch.Tensor, alpha: float, limit: float, alternating: 
     return out
 
 
-def row_gate_add_(y: torch.Tensor, rows: torch.Tensor, z: torch.Tensor, col: int) -> torch.Tensor:
-    """y[r] += sigmoid(z[r, col]) * rows[r]: y float32 [R, H], z float32 [R, *]."""
+def row_gate_add_(y: torch.Tensor, rows: torch.Tensor, z: torch.Tensor, col: int,
+                  extra: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[r] += sigmoid(z[r, col]) * rows[r] (+ extra[r]): y, extra float32 [R, H], z float32 [R, *]."""
     R, H = y.shape
     st = native.lib().rfx_row_gate_add(_chk(y, "y", torch.float32), _chk(rows, "rows"), dt_code(rows.dtype),
-                                       _chk(z, "z", torch.float32), z.shape[1], int(col), R, H, _stream())
+                                       _chk(z, "z", torch.float32), z.shape[1], int(col),
+                                       _chk(extra, "extra", torch.float32), R, H, _stream())
     native.check(st, "row_gate_add")
     return y
 
@@ -1089,19 +1091,22 @@ def conv_state_update(proj: torch.Tensor, col0: int, channels: int, bias: Option
 def conv_qkv_post(proj: torch.Tensor, bias: Optional[torch.Tensor], filters_t: torch.Tensor,
                   state: Optional[torch.Tensor], batch, k_pages, v_pages, page_table, page_size: int, nq: int,
                   nkv: int, dim: int, vdim: int, pad: int, temp_coef: float, temp_every: int, writes_cache: bool,
-                  out_dtype: torch.dtype) -> torch.Tensor:
+                  out_dtype: torch.dtype, col0: int = 0) -> torch.Tensor:
     """The stacked q | k | v columns of `proj` (float32) plus `bias` through
     their short convolutions (`filters_t` float32 [taps, channels]); q times the
     temperature 1 + coef * ln(floor((p + 1) / every) + 1) at position p, out as
     [R, nq * pad]; k and v into the cache at the rows' positions, heads `pad`
-    wide (zeros beyond `dim` and `vdim`)."""
+    wide (zeros beyond `dim` and `vdim`).  `col0`: where the q | k | v columns
+    begin in `proj` (a product stacked with others')."""
     R = proj.shape[0]
     taps = filters_t.shape[0]
     if filters_t.shape[1] != nq * dim + nkv * (dim + vdim):
         raise InvalidInput("conv_qkv_post: the filters must be [taps, channels of q, k and v]")
     q = _new((R, nq * pad), out_dtype, proj.device)
+    if not (0 <= col0 <= proj.shape[1] - filters_t.shape[1]):
+        raise InvalidInput("conv_qkv_post: the q | k | v columns do not fit into proj")
     st = native.lib().rfx_conv_qkv_post(
-        _chk(proj, "proj", torch.float32), proj.shape[1], _chk(bias, "bias", torch.float32),
+        _chk(proj, "proj", torch.float32) + 4 * int(col0), proj.shape[1], _chk(bias, "bias", torch.float32),
         _chk(filters_t, "filters_t", torch.float32), taps, _chk(state, "state", torch.float32),
         state.stride(0) if state is not None else 0, _chk(batch.row_pos, "row_pos", torch.int32),
         _chk(batch.row_slot, "row_slot", torch.int32), q.data_ptr(), _chk(k_pages, "k_pages", out_dtype),
@@ -1117,7 +1122,7 @@ RGLRU_CHUNK_MIN_ROWS = _env_int("REFLEX_B200_RGLRU_CHUNK_MIN_ROWS", 16, 1, 1 << 
 
 def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.Tensor, decay_scale: float,
                proj: torch.Tensor, y_off: int, y_bias, state: torch.Tensor, state_off: int, batch, blocks: int,
-               out_dtype: torch.dtype, max_rows: Optional[int] = None) -> torch.Tensor:
+               out_dtype: torch.dtype, max_rows: Optional[int] = None, conv_tail=None) -> torch.Tensor:
     """The gated linear recurrence over the step's rows, sequence by sequence
     (csrc/rglru.cu): `u` float32 [R, W] its input, `gates` float32 [R, blocks,
     2 W / blocks] the two gates' pre-activations, `proj` holds the other
@@ -1125,9 +1130,13 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.
     state_off : state_off + W]`.  Returns S * gelu_tanh(y), [R, W].  `max_rows`:
     the most rows any sequence brings; from `RGLRU_CHUNK_MIN_ROWS` on the kernel
     that folds 128 rows at a time runs, else the row-by-row walk: the same
-    function, rounded differently."""
+    function, rounded differently.  `conv_tail` = (x_off, x_bias, taps,
+    tail_off): the kernel also stores the sequences' new last taps - 1 inputs of
+    the convolution that made `u` (columns x_off.. of `proj` plus `x_bias`) at
+    `state[slot, tail_off:]`, what `conv_state_update` does in a launch of its own."""
     R, W = u.shape
     chunked = max_rows is not None and max_rows >= RGLRU_CHUNK_MIN_ROWS
+    x_off, x_bias, taps, tail_off = conv_tail if conv_tail is not None else (-1, None, 1, 0)
     out = _new((R, W), out_dtype, u.device)
     st = native.lib().rfx_rglru_scan(
         _chk(u, "u", torch.float32), _chk(gates, "gates", torch.float32), _chk(r_bias, "r_bias", torch.float32),
@@ -1136,7 +1145,7 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, r_bias, i_bias, lam: torch.
         _chk(state, "state", torch.float32), state.stride(0), int(state_off),
         _chk(batch.seq_slot, "seq_slot", torch.int32), _chk(batch.seq_row0, "seq_row0", torch.int32),
         batch.seq_slot.numel(), out.data_ptr(), dt_code(out_dtype), W, int(blocks), 1 if chunked else 0,
-        _stream())
+        int(x_off), _chk(x_bias, "x_bias", torch.float32), int(taps), int(tail_off), _stream())
     native.check(st, f"rglru_scan (width={W}, blocks={blocks})")
     return out
 

@@ -91,11 +91,11 @@ _SIGNATURES = {
                               c_int, c_int, c_void_p],
     "rfx_rglru_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                        c_void_p, c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                       c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_void_p],
     "rfx_branch_norm_mean": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                              c_void_p],
     "rfx_glu_clamped": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
-    "rfx_row_gate_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "rfx_row_gate_add": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
     "rfx_stream_concat": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "rfx_logit_finish": [c_void_p, c_longlong, c_float, c_float, c_void_p],
     "rfx_wait_probe": [c_longlong, c_void_p, c_void_p],

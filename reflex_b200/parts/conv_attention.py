@@ -104,21 +104,35 @@ class ConvAttention:
             o = wide.view(o.shape[0], H * pad)
         self.o = o.contiguous()
 
-    def forward(self, x, ctx):
+    def input_weight(self):
+        """The matrix of the mixer's first product, for a caller that stacks it with
+        others of the same input; `adopt_input_weight` hands back this mixer's rows of
+        the stacked matrix, so that the weights are held once."""
+        return self.qkv
+
+    def adopt_input_weight(self, rows: torch.Tensor) -> None:
+        self.qkv = rows
+
+    def forward(self, x, ctx, proj=None):
         """-> (W_o attention, b_o): the output projection's bias is left to the
-        caller's next kernel (None when the mixer has none)."""
+        caller's next kernel (None when the mixer has none).  `proj` = (float32
+        rows, first column): the first product, already made by the caller as part
+        of a stacked one."""
         s = self.spec
         kv, batch = ctx.kv, ctx.batch
         state = ctx.state if self.taps > 1 else None
         state2d = state.view(state.shape[0], -1) if state is not None else None
-        proj = ops.linear(x, self.qkv, out_dtype=torch.float32)
-        ops.prof_mark("qkv_gemm")
+        if proj is None:
+            proj, col0 = ops.linear(x, self.qkv, out_dtype=torch.float32), 0
+            ops.prof_mark("qkv_gemm")
+        else:
+            proj, col0 = proj
         q = ops.conv_qkv_post(proj, self.bias, self.filters, state2d, batch, kv.k_pages, kv.v_pages,
                               kv.page_table, kv.page_size, s.num_heads, s.num_kv_heads, s.head_dim,
                               s.value_dim, self.pad, self.temp_coef, self.temp_every, ctx.writes_cache,
-                              self.dtype)
+                              self.dtype, col0=col0)
         if state2d is not None:
-            ops.conv_state_update(proj, 0, self.channels, self.bias, self.taps, state2d, batch)
+            ops.conv_state_update(proj, col0, self.channels, self.bias, self.taps, state2d, batch)
         ops.prof_mark("conv_post")
         attn = ops.attention(q, kv.k_pages, kv.v_pages, kv.page_table, kv.page_size, batch, s.num_heads,
                              s.num_kv_heads, self.pad, s.window, s.scale, sink=self.sink, slopes=self.slopes)

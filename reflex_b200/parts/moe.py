@@ -88,7 +88,11 @@ class MixtureOfExperts:
             self.shared_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
             self.shared_down = dev(tensors["shared_down"]).contiguous()
 
-    def forward(self, x, residual=None):
+    supports_onto = True
+
+    def forward(self, x, residual=None, onto=None):
+        """`onto`: a 32-bit delta another part made from the same input (a mixer
+        beside this feed-forward); the result is added onto it and it is returned."""
         logits = ops.linear(x, self.router, out_dtype=torch.float32)  # [rows, experts (+ the shared gate)]
         ids, wts = ops.moe_route(logits, self.router_bias, self.top, experts=self.experts, scores=self.scores)
         ops.prof_mark("moe_router")
@@ -98,6 +102,11 @@ class MixtureOfExperts:
         if self.shared_ff:
             act = ops.glu_clamped(ops.linear(x, self.shared_gate_up), self.alpha, self.shared_limit,
                                   alternating=True)
-            ops.row_gate_add_(out, ops.linear(act, self.shared_down, out_dtype=torch.float32), logits, self.experts)
+            shared = ops.linear(act, self.shared_down, out_dtype=torch.float32)
+            if onto is not None:  # one launch adds both the experts' sum and the gated shared expert
+                ops.row_gate_add_(onto, shared, logits, self.experts, extra=out)
+                ops.prof_mark("moe_shared")
+                return onto
+            ops.row_gate_add_(out, shared, logits, self.experts)
             ops.prof_mark("moe_shared")
-        return out
+        return out if onto is None else ops.add_(onto, out)

@@ -6,7 +6,10 @@ branches are registered mixers of any kind, named by the spec's `left` and
 `right` parameters; what they keep in the cache is asked for together (a tuple
 of their specs) and handed to each in turn.  A branch may return `(delta,
 bias)`: a bias of its last product that this part's kernel adds before the
-norm.
+norm.  Branches that offer the matrix of their first product (`input_weight`,
+`adopt_input_weight`, `forward(..., proj=)`) get it stacked with the other's:
+one product of the shared input serves both, each reads its own columns, and
+the stacked matrix is the only copy of those weights.
 """
 
 from __future__ import annotations
@@ -37,6 +40,8 @@ class PairMixer:
         self.eps = float(spec.param("eps"))
         self.branches = [MIXERS.get(spec.param(side).kind)(spec.param(side), dtype, device) for side in self.SIDES]
         self.weights = [None, None]
+        self.stacked = None   # both branches' first matrices, one above the other
+        self.first_col = [0, 0]
 
     @property
     def capturable(self) -> bool:
@@ -60,19 +65,32 @@ class PairMixer:
         for i, (side, branch) in enumerate(zip(self.SIDES, self.branches)):
             branch.bind({role[len(side) + 1:]: t for role, t in tensors.items() if role.startswith(side + "/")})
             self.weights[i] = tensors[f"{side}_out"].to(device=self.device, dtype=torch.float32).contiguous()
+        if all(hasattr(b, "input_weight") and hasattr(b, "adopt_input_weight") for b in self.branches):
+            parts = [b.input_weight() for b in self.branches]
+            if all(p is not None and p.dtype == parts[0].dtype and p.shape[1] == parts[0].shape[1] for p in parts):
+                self.stacked = torch.cat(parts, dim=0).contiguous()
+                row = 0
+                for i, (b, p) in enumerate(zip(self.branches, parts)):
+                    self.first_col[i] = row
+                    b.adopt_input_weight(self.stacked[row:row + p.shape[0]])
+                    row += p.shape[0]
 
     def forward(self, x, ctx):
         from ..engine.model import RunContext
 
         views = list(ctx.parts) if ctx.parts is not None else [v for v in (ctx.kv, ctx.state) if v is not None]
         outs = []
-        for branch in self.branches:
+        proj = None
+        if self.stacked is not None:
+            proj = ops.linear(x, self.stacked, out_dtype=torch.float32)
+            ops.prof_mark("qkv_gemm")
+        for bi, branch in enumerate(self.branches):
             n = len(_as_tuple(branch.cache_spec() if hasattr(branch, "cache_spec") else None))
             mine, views = views[:n], views[n:]
             sub = RunContext(batch=ctx.batch, writes_cache=ctx.writes_cache, entry=ctx.entry, parts=mine)
             sub.kv = next((v for v in mine if not isinstance(v, torch.Tensor)), None)
             sub.state = next((v for v in mine if isinstance(v, torch.Tensor)), None)
-            r = branch.forward(x, sub)
+            r = branch.forward(x, sub) if proj is None else branch.forward(x, sub, proj=(proj, self.first_col[bi]))
             outs.append(r if isinstance(r, tuple) else (r, None))
         (a, a_bias), (b, b_bias) = outs
         if b_bias is not None:  # the kernel takes one bias: give it the branch that has one

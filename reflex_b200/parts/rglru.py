@@ -83,14 +83,28 @@ class GatedLinearRecurrence:
         self.lam = f32(tensors["lam"])
         self.o = dev(tensors["o_proj"]).contiguous()
 
-    def forward(self, x, ctx):
+    def input_weight(self):
+        """The matrix of the mixer's first product, for a caller that stacks it with
+        others of the same input; `adopt_input_weight` hands back this mixer's rows of
+        the stacked matrix, so that the weights are held once."""
+        return self.yx
+
+    def adopt_input_weight(self, rows: torch.Tensor) -> None:
+        self.yx = rows
+
+    def forward(self, x, ctx, proj=None):
+        """`proj` = (float32 rows, first column): the first product, already made by
+        the caller as part of a stacked one."""
         batch, state, Wr = ctx.batch, ctx.state, self.width
-        proj = ops.linear(x, self.yx, out_dtype=torch.float32)  # [rows, y | x]
-        ops.prof_mark("qkv_gemm")
+        if proj is None:
+            proj, y0 = ops.linear(x, self.yx, out_dtype=torch.float32), 0  # [rows, y | x]
+            ops.prof_mark("qkv_gemm")
+        else:
+            proj, y0 = proj
+        x0 = y0 + Wr
         many = self.gates_lo is not None and x.shape[0] > ops.HEADS_LINEAR_MAX_ROWS
-        u = ops.short_conv(proj, Wr, Wr, self.x_bias, self.filters, self.conv_bias,
+        u = ops.short_conv(proj, x0, Wr, self.x_bias, self.filters, self.conv_bias,
                            state if self.taps > 1 else None, batch, also_bf16=many)
-        ops.conv_state_update(proj, Wr, Wr, self.x_bias, self.taps, state, batch)
         ops.prof_mark("conv_post")
         if many:
             u, u_lo = u
@@ -98,9 +112,10 @@ class GatedLinearRecurrence:
         else:
             gates = ops.heads_linear(u, self.gates)  # [rows, blocks * 2K], 32-bit
         ops.prof_mark("rglru_gates")
-        act = ops.rglru_scan(u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay_scale, proj, 0,
+        # the recurrence's kernel also stores the convolution's new last inputs (it runs after it)
+        act = ops.rglru_scan(u, gates, self.gate_a_bias, self.gate_i_bias, self.lam, self.decay_scale, proj, y0,
                              self.y_bias, state, (self.taps - 1) * Wr, batch, self.blocks, self.dtype,
-                             max_rows=batch.max_new)
+                             max_rows=batch.max_new, conv_tail=(x0, self.x_bias, self.taps, 0))
         ops.prof_mark("rglru_scan")
         out = ops.linear(act, self.o, out_dtype=torch.float32)
         ops.prof_mark("o_proj")

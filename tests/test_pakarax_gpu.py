@@ -261,6 +261,32 @@ def test_gated_recurrence_carried_through_its_state(W, blocks, out_dtype, chunke
 
 
 @pytest.mark.parametrize("chunked", [False, True])
+@pytest.mark.parametrize("taps", [2, 4])
+def test_the_recurrence_kernel_also_keeps_the_convolutions_last_inputs(chunked, taps):
+    """Given the convolution's columns, the recurrence's kernel leaves the same
+    last inputs in the state as `conv_state_update` does, for steps shorter and
+    longer than the filter."""
+    g = torch.Generator().manual_seed(taps)
+    W, ld, x_off = 12, 40, 20
+    xb = torch.randn(W, generator=g)
+    lam = torch.randn(W, generator=g)
+    T = taps - 1
+    a, b_ = torch.zeros(4, T * W + W, device=DEV), torch.zeros(4, T * W + W, device=DEV)
+    for n in (1, 2, 7, 1, 140, 3):
+        batch = FakeBatch([[0] * n, [0] * 2], [2, 0], [0, 0])
+        R = n + 2
+        proj = torch.randn(R, ld, generator=g).to(DEV)
+        u, gates = torch.randn(R, W, generator=g).to(DEV), torch.randn(R, 2 * W, generator=g).to(DEV)
+        ops().rglru_scan(u, gates, None, None, lam.to(DEV), 8.0, proj, 0, None, a, T * W, batch, 1, torch.float32,
+                         max_rows=10 ** 6 if chunked else None, conv_tail=(x_off, xb.to(DEV), taps, 0))
+        ops().rglru_scan(u, gates, None, None, lam.to(DEV), 8.0, proj, 0, None, b_, T * W, batch, 1, torch.float32,
+                         max_rows=10 ** 6 if chunked else None)
+        ops().conv_state_update(proj, x_off, W, xb.to(DEV), taps, b_, batch)
+        assert torch.equal(a, b_)
+    assert float(a[:, :T * W].abs().max()) > 0
+
+
+@pytest.mark.parametrize("chunked", [False, True])
 def test_a_slow_decay_keeps_its_digits(chunked):
     """a within 1e-6 of one: sqrt(1 - a^2) must not be lost to rounding, and S
     builds up over a thousand steps as the closed form says."""
@@ -323,7 +349,10 @@ def test_stream_mix_input_row_gates_and_the_logit_cap():
                            torch.cat([x, x0], dim=1).to(dt).float())
     y, s, z = torch.randn(R, H, generator=g), torch.randn(R, H, generator=g), torch.randn(R, 4, generator=g) * 3
     out = ops().row_gate_add_(y.clone().to(DEV), s.to(DEV), z.to(DEV), 3)
-    assert relerr(out, y.double().numpy() + pp.sigmoid(z.double().numpy()[:, 3:4]) * s.double().numpy()) < 3e-6
+    want = y.double().numpy() + pp.sigmoid(z.double().numpy()[:, 3:4]) * s.double().numpy()
+    assert relerr(out, want) < 3e-6
+    out = ops().row_gate_add_(y.clone().to(DEV), s.to(DEV), z.to(DEV), 3, extra=x0.to(DEV))
+    assert relerr(out, want + x0.double().numpy()) < 3e-6
     lg = torch.randn(3, 50, generator=g) * 40
     out = ops().logit_finish_(lg.clone().to(DEV), 0.5, 30.0)
     assert relerr(out, 30.0 * np.tanh(lg.double().numpy() * 0.5 / 30.0)) < 3e-6
