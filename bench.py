@@ -390,7 +390,7 @@ def design_comparison(args) -> int:
             for q in seqs:
                 eng.close(q)
             eng.check_errors()
-            weight_bytes = sum(t.numel() * t.element_size() for t in _model_tensors(lm))
+            weight_bytes = sum(t.untyped_storage().nbytes() for t in _model_tensors(lm))
             row[design] = {"prefill_ms": pms, "prefill_tok_s": T * 1000.0 / pms, "decode_ms": dms,
                            "decode_tok_s": B * 1000.0 / dms, "decode_launches": launches, "finite": finite,
                            "weight_bytes": weight_bytes, "phases_prefill_ms": phases_prefill,
@@ -417,8 +417,10 @@ def _model_tensors(lm):
 
     def walk(o, depth=0):
         if isinstance(o, torch.Tensor):
-            if o.is_cuda and o.data_ptr() not in seen:
-                seen.add(o.data_ptr())
+            # by storage: a part's rows of a stacked matrix are a view, not more weights
+            key = o.untyped_storage().data_ptr()
+            if o.is_cuda and key not in seen:
+                seen.add(key)
                 out.append(o)
         elif isinstance(o, (list, tuple)):
             for x in o:

@@ -216,7 +216,10 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
     const int bytes = width * (int)sizeof(T);
     if (scale) {
         const float sc = scale[p];
-        for (int c = threadIdx.x; c < width; c += blockDim.x) st<T>(dst, c, ld<T>(src, c) * sc);
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x)
+            st<T>(dst, c, ld<T>(src, c) * sc);
+    } else if (blockIdx.y > 0) {
+        return;  // the plain copy is one block's
     } else if ((bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
         for (int c = threadIdx.x; c < bytes / 16; c += blockDim.x)
             reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
@@ -243,7 +246,7 @@ __global__ void moe_combine_kernel(const T* __restrict__ yg, const int* __restri
                                    const float* __restrict__ wts, float* __restrict__ y, int top, int width) {
     pdl_prologue();
     const int r = blockIdx.x;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         float total = 0.0f;
         for (int k = 0; k < top; ++k)
             total = fmaf(wts ? wts[(size_t)r * top + k] : 1.0f,
@@ -266,11 +269,20 @@ extern "C" int rfx_moe_gather(const void* x, const int* place, const float* scal
                               int n_pairs, int top, int width, void* stream) {
     if (n_pairs <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    // a scaled copy of few rows: a thread an element, so that every load is in flight at once
+    int gy = 1;
+    if (scale) {
+        gy = (width + 127) / 128;
+        const int most = sm_count() * 8 / n_pairs;
+        if (gy > most) gy = most;
+        if (gy < 1) gy = 1;
+    }
+    dim3 grid(n_pairs, gy);
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(moe_gather_kernel<float>, n_pairs, 128, 0, s, (const float*)x, place, scale, (float*)xg, top,
+        RFX_LAUNCH(moe_gather_kernel<float>, grid, 128, 0, s, (const float*)x, place, scale, (float*)xg, top,
                    width);
     else if (dt == RFX_DT_BF16)
-        RFX_LAUNCH(moe_gather_kernel<__nv_bfloat16>, n_pairs, 128, 0, s, (const __nv_bfloat16*)x, place, scale,
+        RFX_LAUNCH(moe_gather_kernel<__nv_bfloat16>, grid, 128, 0, s, (const __nv_bfloat16*)x, place, scale,
                    (__nv_bfloat16*)xg, top, width);
     else
         return RFX_ERR_BAD_ARG;
@@ -295,10 +307,15 @@ extern "C" int rfx_moe_combine(const void* yg, int dt, const int* place, const f
                                int top, int width, void* stream) {
     if (R <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    int gy = (width + 255) / 256;  // few rows: a thread an element
+    const int most = sm_count() * 8 / R;
+    if (gy > most) gy = most;
+    if (gy < 1) gy = 1;
+    dim3 grid(R, gy);
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(moe_combine_kernel<float>, R, 256, 0, s, (const float*)yg, place, wts, y, top, width);
+        RFX_LAUNCH(moe_combine_kernel<float>, grid, 256, 0, s, (const float*)yg, place, wts, y, top, width);
     else if (dt == RFX_DT_BF16)
-        RFX_LAUNCH(moe_combine_kernel<__nv_bfloat16>, R, 256, 0, s, (const __nv_bfloat16*)yg, place, wts, y, top,
+        RFX_LAUNCH(moe_combine_kernel<__nv_bfloat16>, grid, 256, 0, s, (const __nv_bfloat16*)yg, place, wts, y, top,
                    width);
     else
         return RFX_ERR_BAD_ARG;

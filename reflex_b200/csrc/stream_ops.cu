@@ -17,6 +17,38 @@ namespace {
 
 using namespace rfx;
 
+// rows of up to PER * blockDim elements: a thread's elements stay in registers, all
+// its loads are in flight together and global memory is read once
+template <int PER>
+__global__ void __launch_bounds__(1024)
+branch_norm_mean_reg_kernel(const float* __restrict__ a, const float* __restrict__ a_bias,
+                            const float* __restrict__ wa, const float* __restrict__ b,
+                            const float* __restrict__ wb, float eps, float* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    pdl_prologue();
+    const size_t r = blockIdx.x;
+    float x[PER], y[PER];
+    float sa = 0.0f, sb = 0.0f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = i * blockDim.x + threadIdx.x;
+        x[i] = c < H ? a[r * H + c] + (a_bias ? a_bias[c] : 0.0f) : 0.0f;
+        y[i] = c < H ? b[r * H + c] : 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        sa = fmaf(x[i], x[i], sa);
+        sb = fmaf(y[i], y[i], sb);
+    }
+    const float ra = rsqrtf(block_sum(sa, scratch) / (float)H + eps);
+    const float rb = rsqrtf(block_sum(sb, scratch) / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int c = i * blockDim.x + threadIdx.x;
+        if (c < H) out[r * H + c] = 0.5f * fmaf(x[i] * ra, wa[c], (y[i] * rb) * wb[c]);
+    }
+}
+
 __global__ void __launch_bounds__(256)
 branch_norm_mean_kernel(const float* __restrict__ a, const float* __restrict__ a_bias,
                         const float* __restrict__ wa, const float* __restrict__ b,
@@ -107,7 +139,7 @@ __global__ void row_gate_add_kernel(float* __restrict__ y, const T* __restrict__
     pdl_prologue();
     const size_t r = blockIdx.x;
     const float gate = 1.0f / (1.0f + expf(-z[r * ldz + col]));
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x) {
         float v = y[r * H + c];
         if (extra) v += extra[r * H + c];
         y[r * H + c] = fmaf(gate, ld<T>(s, r * H + c), v);
@@ -119,7 +151,7 @@ __global__ void stream_concat_kernel(const float* __restrict__ x, const TD* __re
                                      const float* __restrict__ x0, TO* __restrict__ out, int H) {
     pdl_prologue();
     const size_t r = blockIdx.x;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < H; c += gridDim.y * blockDim.x) {
         float v = x[r * H + c];
         if (delta) v += ld<TD>(delta, r * H + c);
         st<TO>(out, r * 2 * H + c, v);
@@ -136,6 +168,15 @@ __global__ void logit_finish_kernel(float* __restrict__ z, size_t n, float scale
     }
 }
 
+// blocks along a row for kernels that take a row's elements independently: few rows get a
+// thread an element (every load in flight at once), many rows walk their row
+int row_chunks(int R, int H) {
+    int g = (H + 255) / 256;
+    const int most = sm_count() * 8 / (R < 1 ? 1 : R);
+    if (g > most) g = most;
+    return g < 1 ? 1 : g;
+}
+
 int blocks_for(size_t n) {
     size_t b = (n + 255) / 256;
     const size_t most = (size_t)sm_count() * 16;
@@ -147,8 +188,12 @@ int blocks_for(size_t n) {
 extern "C" int rfx_branch_norm_mean(const float* a, const float* a_bias, const float* wa, const float* b,
                                     const float* wb, float eps, float* out, int R, int H, void* stream) {
     if (R <= 0 || H <= 0) return 0;
-    RFX_LAUNCH(branch_norm_mean_kernel, R, H >= 1024 ? 256 : 128, 0, (cudaStream_t)stream, a, a_bias, wa, b, wb,
-               eps, out, H);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (H <= 4 * 128) RFX_LAUNCH(branch_norm_mean_reg_kernel<4>, R, 128, 0, s, a, a_bias, wa, b, wb, eps, out, H);
+    else if (H <= 4 * 256) RFX_LAUNCH(branch_norm_mean_reg_kernel<4>, R, 256, 0, s, a, a_bias, wa, b, wb, eps, out, H);
+    else if (H <= 4 * 512) RFX_LAUNCH(branch_norm_mean_reg_kernel<4>, R, 512, 0, s, a, a_bias, wa, b, wb, eps, out, H);
+    else if (H <= 8 * 1024) RFX_LAUNCH(branch_norm_mean_reg_kernel<8>, R, 1024, 0, s, a, a_bias, wa, b, wb, eps, out, H);
+    else RFX_LAUNCH(branch_norm_mean_kernel, R, 256, 0, s, a, a_bias, wa, b, wb, eps, out, H);
     return 0;
 }
 
@@ -177,10 +222,11 @@ extern "C" int rfx_row_gate_add(float* y, const void* s_rows, int dt, const floa
     if (R <= 0 || H <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (dt == RFX_DT_F32)
-        RFX_LAUNCH(row_gate_add_kernel<float>, R, 256, 0, s, y, (const float*)s_rows, z, ldz, col, extra, H);
-    else if (dt == RFX_DT_BF16)
-        RFX_LAUNCH(row_gate_add_kernel<__nv_bfloat16>, R, 256, 0, s, y, (const __nv_bfloat16*)s_rows, z, ldz,
+        RFX_LAUNCH(row_gate_add_kernel<float>, dim3(R, row_chunks(R, H)), 256, 0, s, y, (const float*)s_rows, z, ldz,
                    col, extra, H);
+    else if (dt == RFX_DT_BF16)
+        RFX_LAUNCH(row_gate_add_kernel<__nv_bfloat16>, dim3(R, row_chunks(R, H)), 256, 0, s, y,
+                   (const __nv_bfloat16*)s_rows, z, ldz, col, extra, H);
     else
         return RFX_ERR_BAD_ARG;
     return 0;
@@ -193,7 +239,8 @@ extern "C" int rfx_stream_concat(const float* x, const void* delta, int delta_dt
     const bool dbf = delta && delta_dt == RFX_DT_BF16;
     if (delta && delta_dt != RFX_DT_BF16 && delta_dt != RFX_DT_F32) return RFX_ERR_BAD_ARG;
 #define RFX_GO(TD, TO)                                                                                   \
-    RFX_LAUNCH((stream_concat_kernel<TD, TO>), R, 256, 0, s, x, (const TD*)delta, x0, (TO*)out, H)
+    RFX_LAUNCH((stream_concat_kernel<TD, TO>), dim3(R, row_chunks(R, H)), 256, 0, s, x, (const TD*)delta, x0, \
+               (TO*)out, H)
     if (out_dt == RFX_DT_F32) {
         if (dbf) RFX_GO(__nv_bfloat16, float);
         else RFX_GO(float, float);

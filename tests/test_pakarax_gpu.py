@@ -308,7 +308,7 @@ def test_a_slow_decay_keeps_its_digits(chunked):
 
 def test_two_branches_normed_and_averaged():
     g = torch.Generator().manual_seed(0)
-    for R, H in ((1, 64), (5, 100), (70, 1024)):
+    for R, H in ((1, 64), (5, 100), (70, 1024), (3, 5000), (2, 9000)):  # every form of the kernel
         a, b = torch.randn(R, H, generator=g) * 3, torch.randn(R, H, generator=g) * 0.01
         ab, wa, wb = torch.randn(H, generator=g), torch.rand(H, generator=g) + 0.5, torch.rand(H, generator=g)
         ref = 0.5 * (pp.rms_norm(a.double().numpy() + ab.double().numpy(), wa.double().numpy(), 1e-5)
