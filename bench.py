@@ -425,7 +425,7 @@ def _model_tensors(lm):
         elif isinstance(o, (list, tuple)):
             for x in o:
                 walk(x, depth + 1)
-        elif hasattr(o, "__dict__") and depth < 4:
+        elif hasattr(o, "__dict__") and depth < 8:  # a mixer may hold mixers of its own
             for x in vars(o).values():
                 walk(x, depth + 1)
 

@@ -216,6 +216,22 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
     const int bytes = width * (int)sizeof(T);
     if (scale) {
         const float sc = scale[p];
+        if constexpr (sizeof(T) == 2) {
+            if ((bytes & 15) == 0 && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15) == 0) {
+                // eight elements a thread and step
+                for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width / 8; c += gridDim.y * blockDim.x) {
+                    uint4 v = reinterpret_cast<const uint4*>(src)[c];
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float2 f = __bfloat1622float2(h[j]);
+                        h[j] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+                    }
+                    reinterpret_cast<uint4*>(dst)[c] = v;
+                }
+                return;
+            }
+        }
         for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x)
             st<T>(dst, c, ld<T>(src, c) * sc);
     } else if (blockIdx.y > 0) {

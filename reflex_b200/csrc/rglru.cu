@@ -32,6 +32,27 @@ namespace {
 using namespace rfx;
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+// For results that are rounded to bfloat16 anyway (the serving path): the fast
+// exponential, division and hyperbolic tangent, a few units in the last place of
+// 32 bits (the tangent 2^-11) off, far below that rounding.  The 32-bit path keeps
+// the exact forms.
+template <typename TO> __device__ __forceinline__ float sigmoid_for(float z) {
+    if constexpr (sizeof(TO) == 2) return __fdividef(1.0f, 1.0f + __expf(-z));
+    else return sigmoid_f(z);
+}
+template <typename TO> __device__ __forceinline__ float exp_for(float z) {
+    if constexpr (sizeof(TO) == 2) return __expf(z);
+    else return expf(z);
+}
+template <typename TO> __device__ __forceinline__ float gelu_tanh_for(float z) {
+    if constexpr (sizeof(TO) == 2) {
+        float t;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        return 0.5f * z * (1.0f + t);
+    } else {
+        return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    }
+}
 __device__ __forceinline__ float softplus_f(float z) { return fmaxf(z, 0.0f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
@@ -154,11 +175,11 @@ rglru_chunk_kernel(const float* __restrict__ u, const float* __restrict__ gates,
         for (int j = 0; j < CH_ROWS; ++j) {
             const int t = tile + grp * CH_ROWS + j;
             if (t < n) {
-                const float r = sigmoid_f(in[j].r + rb);
-                const float i = sigmoid_f(in[j].i + ib);
-                Y[j] = gelu_tanh_f(in[j].y + yb);
+                const float r = sigmoid_for<TO>(in[j].r + rb);
+                const float i = sigmoid_for<TO>(in[j].i + ib);
+                Y[j] = gelu_tanh_for<TO>(in[j].y + yb);
                 const float log_a = rate * r;
-                const float a = expf(log_a);
+                const float a = exp_for<TO>(log_a);
                 acc = fmaf(a, acc, sqrtf(-expm1f(2.0f * log_a)) * (i * in[j].u));
                 p *= a;
             } else {

@@ -38,13 +38,11 @@ constexpr int MAX_TAPS = 16;
 // the rows before are loaded side by side, not one after the other's answer
 __device__ __forceinline__ int rows_before(const int* __restrict__ row_slot, int r, int cap) {
     const int slot = row_slot[r];
-    bool same[MAX_TAPS - 1];
-#pragma unroll
-    for (int j = 0; j < MAX_TAPS - 1; ++j) same[j] = (j < cap && r - j - 1 >= 0) ? row_slot[r - j - 1] == slot : false;
-    int t = 0;
-#pragma unroll
-    for (int j = 0; j < MAX_TAPS - 1; ++j)
-        if (t == j && same[j]) t = j + 1;
+    int t = cap;  // the nearest row back that is not this sequence's ends the count (no early exit: no chain)
+    for (int j = cap - 1; j >= 0; --j) {
+        const bool same = r - j - 1 >= 0 && row_slot[r - j - 1] == slot;
+        if (!same) t = j;
+    }
     return t;
 }
 
@@ -226,7 +224,7 @@ extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* 
     const int by4 = C % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && slot_stride % 4 == 0 && aligned16(proj) &&
                     aligned16(bias) && aligned16(w) && aligned16(cbias) && aligned16(state) && aligned16(out) &&
                     ((reinterpret_cast<uintptr_t>(out_lo) & 7) == 0);
-    dim3 grid(R, chunks(by4 ? C / 4 : C, 256));
+    dim3 grid(R, chunks(by4 ? C / 8 : C, 256));  // by fours: two units a thread, the row's own work shared
     RFX_LAUNCH(short_conv_kernel, grid, 256, 0, (cudaStream_t)stream, proj, ld, col0, bias, w, cbias, taps,
                state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4);
     return 0;
@@ -246,7 +244,7 @@ extern "C" int rfx_conv_qkv_post(const float* proj, int ld, const float* bias, c
     const int by4 = dim % 4 == 0 && vdim % 4 == 0 && pad % 4 == 0 && ld % 4 == 0 && slot_stride % 4 == 0 &&
                     aligned16(proj) && aligned16(bias) && aligned16(w) && aligned16(state) && aligned16(q_out) &&
                     aligned16(k_pages) && aligned16(v_pages);
-    dim3 grid(R, chunks((nq + 2 * nkv) * pad / (by4 ? 4 : 1), 256));
+    dim3 grid(R, chunks((nq + 2 * nkv) * pad / (by4 ? 8 : 1), 256));  // by fours: two units a thread
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dt == RFX_DT_F32)
         RFX_LAUNCH(conv_qkv_post_kernel<float>, grid, 256, 0, s, proj, ld, bias, w, taps, state,
