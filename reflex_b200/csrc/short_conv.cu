@@ -224,7 +224,9 @@ extern "C" int rfx_short_conv(const float* proj, int ld, int col0, const float* 
     const int by4 = C % 4 == 0 && ld % 4 == 0 && col0 % 4 == 0 && slot_stride % 4 == 0 && aligned16(proj) &&
                     aligned16(bias) && aligned16(w) && aligned16(cbias) && aligned16(state) && aligned16(out) &&
                     ((reinterpret_cast<uintptr_t>(out_lo) & 7) == 0);
-    dim3 grid(R, chunks(by4 ? C / 8 : C, 256));  // by fours: two units a thread, the row's own work shared
+    // by fours, many rows: two units a thread share the row's own work; few rows: a unit a thread,
+    // so that a decode step's loads are all in flight at once
+    dim3 grid(R, chunks(by4 ? C / (R >= 256 ? 8 : 4) : C, 256));
     RFX_LAUNCH(short_conv_kernel, grid, 256, 0, (cudaStream_t)stream, proj, ld, col0, bias, w, cbias, taps,
                state, (size_t)slot_stride, row_slot, out, (__nv_bfloat16*)out_lo, C, by4);
     return 0;
@@ -244,7 +246,7 @@ extern "C" int rfx_conv_qkv_post(const float* proj, int ld, const float* bias, c
     const int by4 = dim % 4 == 0 && vdim % 4 == 0 && pad % 4 == 0 && ld % 4 == 0 && slot_stride % 4 == 0 &&
                     aligned16(proj) && aligned16(bias) && aligned16(w) && aligned16(state) && aligned16(q_out) &&
                     aligned16(k_pages) && aligned16(v_pages);
-    dim3 grid(R, chunks((nq + 2 * nkv) * pad / (by4 ? 8 : 1), 256));  // by fours: two units a thread
+    dim3 grid(R, chunks((nq + 2 * nkv) * pad / (by4 ? (R >= 256 ? 8 : 4) : 1), 256));  // as in rfx_short_conv
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dt == RFX_DT_F32)
         RFX_LAUNCH(conv_qkv_post_kernel<float>, grid, 256, 0, s, proj, ld, bias, w, taps, state,
