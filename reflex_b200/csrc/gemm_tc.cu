@@ -96,7 +96,25 @@ struct Fuse {
     __nv_bfloat16* v_pages;
     rfx::PagedKV cache;
     int nq, nkv_in, head_dim;
+    // EPI 1: act_clamped != 0 makes the gated activation the clamped form,
+    // g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1),
+    // instead of silu(g) u
+    int act_clamped;
+    float act_alpha, act_limit;
 };
+
+// The gated activation of EPI 1 (results rounded to bfloat16 take the fast exponential
+// and division, as `silu_mul_for` does).
+template <typename TO>
+__device__ __forceinline__ float gated_act(float g, float u, const Fuse& f) {
+    if (f.act_clamped) {
+        g = fminf(g, f.act_limit);
+        u = fminf(fmaxf(u, -f.act_limit), f.act_limit);
+        if constexpr (sizeof(TO) == 2) return __fdividef(g, 1.0f + __expf(-f.act_alpha * g)) * (u + 1.0f);
+        else return (g / (1.0f + expf(-f.act_alpha * g))) * (u + 1.0f);
+    }
+    return rfx::silu_mul_for<TO>(g, u);
+}
 
 //  * EPI 3: W is the stacked q/k/v matrix of an attention layer whose head size
 //    is 64 or 128, so a 128-row tile holds whole heads.  The split-K partials are
@@ -560,7 +578,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float f = rstd_s[rr];
                             acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
                         }
-                        const float o0 = silu_mul_for<TO>(acc.x, acc.y), o1 = silu_mul_for<TO>(acc.z, acc.w);
+                        const float o0 = gated_act<TO>(acc.x, acc.y, fuse), o1 = gated_act<TO>(acc.z, acc.w, fuse);
                         if (!dry) store2(y + (size_t)r * (N / 2) + n / 2, o0, o1);
                     }
                 } else if (quads && EPI == 2 && BN <= 64) {
@@ -642,7 +660,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
                         const int r = r0 + rr;
                         if (r < R && n0 + mm + 1 < N && !dry)
-                            rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, silu_mul_for<TO>(g, u));
+                            rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, gated_act<TO>(g, u, fuse));
                     }
                 } else {
                     for (int e = et; e < BN * mw; e += ET) {
@@ -704,7 +722,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float got = __shfl_xor_sync(0xffffffffu, even ? a1 : a0, 1);
                             const float gate = even ? a0 : got, up = even ? got : a1;
                             const int r = r0 + c * 16 + j + (even ? 0 : 1);
-                            const float o = silu_mul_for<TO>(gate, up);
+                            const float o = gated_act<TO>(gate, up, fuse);
                             if (pair_ok && r < R) rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, o);
                         }
                     } else {
@@ -969,6 +987,24 @@ extern "C" int rfx_gemm_bf16_tc(const void* x, const void* W, void* y, int y_dt,
         else { if (pro) RFX_GO(__nv_bfloat16, 1, true); else RFX_GO(__nv_bfloat16, 1, false); }
     }
 #undef RFX_GO
+    return RFX_ERR_BAD_ARG;
+}
+
+// y [R, N / 2] = act(x W^T) for W whose rows alternate gate_j, up_j, with the clamped gated
+// activation g' sigmoid(alpha g') (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit),
+// as the product's epilogue (the counterpart of epilogue 1 of rfx_gemm_bf16_tc).
+extern "C" int rfx_gemm_bf16_tc_glu_clamped(const void* x, const void* W, void* y, int y_dt, int R, int N, int K,
+                                            int ksplit, float alpha, float limit, int* err, void* stream) {
+    if (R <= 0 || N <= 0) return 0;
+    if (int c = check_common(x, W, R, N, K)) return c;
+    if (N & 1) return RFX_ERR_BAD_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    Fuse f{};
+    f.act_clamped = 1;
+    f.act_alpha = alpha;
+    f.act_limit = limit;
+    if (y_dt == RFX_DT_F32) return dispatch<float, 1, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
+    if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 1, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
     return RFX_ERR_BAD_ARG;
 }
 

@@ -843,18 +843,21 @@ MOE_SCORES = {"softmax_top": 0, "sigmoid": 1}
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, experts: Optional[int] = None,
-              scores: str = "softmax_top"):
+              scores: str = "softmax_top", col0: int = 0):
     """Router logits float32 [R, experts] (+ bias) -> ids int32 [R, top], the
     experts with the largest logits, and weights float32 [R, top]: the softmax
     over the chosen logits only ("softmax_top"), or each chosen logit's sigmoid
-    as it is ("sigmoid").  With `experts` only the first that many columns of
-    `logits` are router logits (the rest belongs to the caller)."""
-    R, E = logits.shape
-    ld = E
-    E = E if experts is None else int(experts)
+    as it is ("sigmoid").  With `experts` only that many columns of `logits`,
+    from column `col0` on, are router logits (the rest belongs to the caller: a
+    product stacked with others')."""
+    R, ld = logits.shape
+    E = ld if experts is None else int(experts)
+    if not (0 <= col0 <= ld - E):
+        raise InvalidInput("moe_route: the router's columns do not fit into the logits' rows")
     ids = _new((R, top), torch.int32, logits.device)
     wts = _new((R, top), torch.float32, logits.device)
-    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32), ld, _chk(bias, "bias", torch.float32),
+    st = native.lib().rfx_moe_route(_chk(logits, "logits", torch.float32) + 4 * int(col0), ld,
+                                    _chk(bias, "bias", torch.float32),
                                     ids.data_ptr(), wts.data_ptr(), R, E, int(top), MOE_SCORES[scores], _stream())
     native.check(st, f"moe_route (experts={E}, top={top})")
     return ids, wts
@@ -990,6 +993,27 @@ def glu_clamped(gate_up: torch.Tensor, alpha: float, limit: float, alternating: 
                                       1 if alternating else 0, float(alpha), float(limit), _stream())
     native.check(st, "glu_clamped")
     return out
+
+
+def linear_glu_clamped(x: torch.Tensor, weight_pairs: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
+    """glu_clamped(x @ W.T) for a weight whose rows alternate gate_j, up_j; [R, I]
+    in x's dtype.  For a few bfloat16 rows the activation is the product
+    kernel's epilogue; otherwise product, then `glu_clamped`."""
+    R, K = x.shape
+    if x.dtype == torch.bfloat16 and R <= GEMV_MAX_ROWS and K % 8 == 0 and FUSE_GLU:
+        N = weight_pairs.shape[0]
+        _chk(x, "x", torch.bfloat16)
+        _chk(weight_pairs, "weight", torch.bfloat16)
+        y = _new((R, N // 2), torch.bfloat16, x.device)
+        st = native.lib().rfx_gemm_bf16_tc_glu_clamped(
+            x.data_ptr(), weight_pairs.data_ptr(), y.data_ptr(), BF16, R, N, K, 0, float(alpha), float(limit),
+            device_error_word(x.device).data_ptr(), _stream())
+        native.check(st, f"gemm_bf16_tc_glu_clamped (R={R}, N={N}, K={K})")
+        return y
+    return glu_clamped(linear(x, weight_pairs), alpha, limit, alternating=True)
+
+
+FUSE_GLU = _env_flag("REFLEX_B200_FUSE_GLU", True)  # 0: product and activation apart (tests compare the two)
 
 
 def row_gate_add_(y: torch.Tensor, rows: torch.Tensor, z: torch.Tensor, col: int,

@@ -120,7 +120,11 @@ class PreNormBlock:
 class ParallelBlock(PreNormBlock):
     """n = norm(h); h += mixer(n) + ffn(n): one norm, both sublayers read its
     output, their sum is the layer's delta.  The spec's `feed_forward_norm` is
-    None; a layer without a feed-forward is h += mixer(norm(h))."""
+    None; a layer without a feed-forward is h += mixer(norm(h)).  Where the mixer
+    and the feed-forward both offer the matrix of their first product of the
+    shared input (`input_weight` / `adopt_input_weight` / `forward(..., proj=)`: a
+    pair mixer's stacked projections, a router), the block stacks the two and
+    makes one product for both."""
 
     def __init__(self, spec: LayerSpec, dtype: torch.dtype, device):
         self.spec = spec
@@ -130,6 +134,8 @@ class ParallelBlock(PreNormBlock):
         self.feed_forward_norm = None
         self.feed_forward = (FEED_FORWARDS.get(spec.feed_forward.kind)(spec.feed_forward, dtype, device)
                              if self.has_feed_forward else None)
+        self.stacked = None  # the mixer's and the feed-forward's first matrices, one above the other
+        self.ffn_col = 0
 
     fusable_first_norm = None  # its mixers take plain normed rows
 
@@ -157,6 +163,15 @@ class ParallelBlock(PreNormBlock):
         self.mixer.bind(by_part.get("mixer", {}))
         if self.has_feed_forward:
             self.feed_forward.bind(by_part.get("feed_forward", {}))
+            both = [self.mixer, self.feed_forward]
+            if all(hasattr(p, "input_weight") and hasattr(p, "adopt_input_weight") for p in both):
+                mats = [p.input_weight() for p in both]
+                if (all(m is not None for m in mats) and mats[0].dtype == mats[1].dtype
+                        and mats[0].shape[1] == mats[1].shape[1] and getattr(self.feed_forward, "supports_onto", False)):
+                    self.stacked = torch.cat(mats, dim=0).contiguous()
+                    self.ffn_col = mats[0].shape[0]
+                    self.mixer.adopt_input_weight(self.stacked[:self.ffn_col])
+                    self.feed_forward.adopt_input_weight(self.stacked[self.ffn_col:])
 
     def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
         from .. import ops
@@ -165,6 +180,11 @@ class ParallelBlock(PreNormBlock):
             pending = None  # the stream already holds the sum; this block's parts want plain normed rows
         x = self.mixer_norm(hidden, delta=pending)
         ops.prof_mark("norm")
+        if self.stacked is not None:
+            proj = ops.linear(x, self.stacked, out_dtype=torch.float32)
+            ops.prof_mark("qkv_gemm")
+            delta = self.mixer.forward(x, ctx, proj=(proj, 0))
+            return hidden, self.feed_forward.forward(x, onto=delta, proj=(proj, self.ffn_col))
         delta = self.mixer.forward(x, ctx)
         if self.has_feed_forward:
             if getattr(self.feed_forward, "supports_onto", False):

@@ -101,7 +101,7 @@ class ClampedGLU:
     supports_onto = True
 
     def forward(self, x, residual=None, onto=None):
-        act = ops.glu_clamped(ops.linear(x, self.gate_up), self.alpha, self.limit, alternating=True)
+        act = ops.linear_glu_clamped(x, self.gate_up, self.alpha, self.limit)
         ops.prof_mark("ffn_gate_up")
         if onto is not None:
             # many bfloat16 rows: the product accumulates onto the 32-bit delta

@@ -90,23 +90,37 @@ class MixtureOfExperts:
 
     supports_onto = True
 
-    def forward(self, x, residual=None, onto=None):
+    def input_weight(self):
+        """The router's matrix (with the shared gate's row), for a caller that stacks
+        it with other matrices of the same input; `adopt_input_weight` hands back
+        this part's rows of the stacked matrix."""
+        return self.router
+
+    def adopt_input_weight(self, rows: torch.Tensor) -> None:
+        self.router = rows
+
+    def forward(self, x, residual=None, onto=None, proj=None):
         """`onto`: a 32-bit delta another part made from the same input (a mixer
-        beside this feed-forward); the result is added onto it and it is returned."""
-        logits = ops.linear(x, self.router, out_dtype=torch.float32)  # [rows, experts (+ the shared gate)]
-        ids, wts = ops.moe_route(logits, self.router_bias, self.top, experts=self.experts, scores=self.scores)
+        beside this feed-forward); the result is added onto it and it is returned.
+        `proj` = (float32 rows, first column): the router's product, already made
+        by the caller as part of a stacked one."""
+        if proj is None:
+            logits, col0 = ops.linear(x, self.router, out_dtype=torch.float32), 0  # [rows, experts (+ the shared gate)]
+        else:
+            logits, col0 = proj
+        ids, wts = ops.moe_route(logits, self.router_bias, self.top, experts=self.experts, scores=self.scores,
+                                 col0=col0)
         ops.prof_mark("moe_router")
         out = ops.moe_experts(x, self.up, self.down, ids, wts, self.activation, self.weight_input, self.alpha,
                               self.limit)
         ops.prof_mark("moe_experts")
         if self.shared_ff:
-            act = ops.glu_clamped(ops.linear(x, self.shared_gate_up), self.alpha, self.shared_limit,
-                                  alternating=True)
+            act = ops.linear_glu_clamped(x, self.shared_gate_up, self.alpha, self.shared_limit)
             shared = ops.linear(act, self.shared_down, out_dtype=torch.float32)
             if onto is not None:  # one launch adds both the experts' sum and the gated shared expert
-                ops.row_gate_add_(onto, shared, logits, self.experts, extra=out)
+                ops.row_gate_add_(onto, shared, logits, col0 + self.experts, extra=out)
                 ops.prof_mark("moe_shared")
                 return onto
-            ops.row_gate_add_(out, shared, logits, self.experts)
+            ops.row_gate_add_(out, shared, logits, col0 + self.experts)
             ops.prof_mark("moe_shared")
         return out if onto is None else ops.add_(onto, out)

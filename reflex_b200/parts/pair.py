@@ -75,13 +75,26 @@ class PairMixer:
                     b.adopt_input_weight(self.stacked[row:row + p.shape[0]])
                     row += p.shape[0]
 
-    def forward(self, x, ctx):
+    def input_weight(self):
+        """The stacked matrix, for a caller that stacks it further (a block whose
+        feed-forward reads the same input); None if the branches offered none."""
+        return self.stacked
+
+    def adopt_input_weight(self, rows: torch.Tensor) -> None:
+        self.stacked = rows
+        ends = self.first_col[1:] + [rows.shape[0]]
+        for b, lo, hi in zip(self.branches, self.first_col, ends):
+            b.adopt_input_weight(rows[lo:hi])
+
+    def forward(self, x, ctx, proj=None):
         from ..engine.model import RunContext
 
         views = list(ctx.parts) if ctx.parts is not None else [v for v in (ctx.kv, ctx.state) if v is not None]
         outs = []
-        proj = None
-        if self.stacked is not None:
+        col0 = 0
+        if proj is not None:
+            proj, col0 = proj  # the caller made the product, stacked with more of its own
+        elif self.stacked is not None:
             proj = ops.linear(x, self.stacked, out_dtype=torch.float32)
             ops.prof_mark("qkv_gemm")
         for bi, branch in enumerate(self.branches):
@@ -90,7 +103,8 @@ class PairMixer:
             sub = RunContext(batch=ctx.batch, writes_cache=ctx.writes_cache, entry=ctx.entry, parts=mine)
             sub.kv = next((v for v in mine if not isinstance(v, torch.Tensor)), None)
             sub.state = next((v for v in mine if isinstance(v, torch.Tensor)), None)
-            r = branch.forward(x, sub) if proj is None else branch.forward(x, sub, proj=(proj, self.first_col[bi]))
+            r = (branch.forward(x, sub) if proj is None
+                 else branch.forward(x, sub, proj=(proj, col0 + self.first_col[bi])))
             outs.append(r if isinstance(r, tuple) else (r, None))
         (a, a_bias), (b, b_bias) = outs
         if b_bias is not None:  # the kernel takes one bias: give it the branch that has one

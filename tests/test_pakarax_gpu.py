@@ -337,6 +337,22 @@ def test_clamped_gated_activation(dtype, alternating, I):
     assert abs(float(out[0, 0])) < 1e-6  # a gate far below zero: nothing passes
 
 
+@pytest.mark.parametrize("R,I,K", [(1, 96, 64), (8, 320, 256), (33, 52, 128), (64, 1024, 512)])
+def test_the_activation_as_the_products_epilogue(R, I, K):
+    """A few bfloat16 rows: the product kernel applies the clamped gated activation
+    itself; the same numbers as product, then activation."""
+    g = torch.Generator().manual_seed(R + I)
+    x = torch.randn(R, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * I, K, generator=g) * 0.3).to(torch.bfloat16)  # rows alternate gate, up
+    z = x.double().numpy() @ w.double().numpy().T
+    gc = np.minimum(z[:, 0::2], 0.9)
+    ref = gc * pp.sigmoid(1.702 * gc) * (np.clip(z[:, 1::2], -0.9, 0.9) + 1.0)
+    out = ops().linear_glu_clamped(x.to(DEV), w.to(DEV), 1.702, 0.9)
+    ops().check_device_errors(DEV)
+    assert relerr(out, ref) < 8e-3
+    assert np.abs(ref).max() > 0.5 and (np.abs(z[:, 1::2]) > 0.9).mean() > 0.2  # the clamps bite
+
+
 def test_stream_mix_input_row_gates_and_the_logit_cap():
     g = torch.Generator().manual_seed(2)
     R, H = 5, 24
