@@ -168,10 +168,14 @@ class ParallelBlock(PreNormBlock):
                 mats = [p.input_weight() for p in both]
                 if (all(m is not None for m in mats) and mats[0].dtype == mats[1].dtype
                         and mats[0].shape[1] == mats[1].shape[1] and getattr(self.feed_forward, "supports_onto", False)):
-                    self.stacked = torch.cat(mats, dim=0).contiguous()
+                    # zero rows up to a multiple of 8: the product's rows stay 16-byte aligned, which
+                    # the library's products and the kernels that read four columns a thread want
+                    rows = mats[0].shape[0] + mats[1].shape[0]
+                    pad = torch.zeros((-rows % 8, mats[0].shape[1]), dtype=mats[0].dtype, device=mats[0].device)
+                    self.stacked = torch.cat(mats + [pad], dim=0).contiguous()
                     self.ffn_col = mats[0].shape[0]
                     self.mixer.adopt_input_weight(self.stacked[:self.ffn_col])
-                    self.feed_forward.adopt_input_weight(self.stacked[self.ffn_col:])
+                    self.feed_forward.adopt_input_weight(self.stacked[self.ffn_col:rows])
 
     def forward(self, hidden: torch.Tensor, pending, ctx, next_norm=None):
         from .. import ops

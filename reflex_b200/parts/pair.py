@@ -42,6 +42,7 @@ class PairMixer:
         self.weights = [None, None]
         self.stacked = None   # both branches' first matrices, one above the other
         self.first_col = [0, 0]
+        self.part_rows = [0, 0]
 
     @property
     def capturable(self) -> bool:
@@ -68,10 +69,14 @@ class PairMixer:
         if all(hasattr(b, "input_weight") and hasattr(b, "adopt_input_weight") for b in self.branches):
             parts = [b.input_weight() for b in self.branches]
             if all(p is not None and p.dtype == parts[0].dtype and p.shape[1] == parts[0].shape[1] for p in parts):
-                self.stacked = torch.cat(parts, dim=0).contiguous()
+                # zero rows up to a multiple of 8, so that the product's rows stay 16-byte aligned
+                rows = sum(p.shape[0] for p in parts)
+                pad = torch.zeros((-rows % 8, parts[0].shape[1]), dtype=parts[0].dtype, device=parts[0].device)
+                self.stacked = torch.cat(parts + [pad], dim=0).contiguous()
                 row = 0
                 for i, (b, p) in enumerate(zip(self.branches, parts)):
                     self.first_col[i] = row
+                    self.part_rows[i] = p.shape[0]
                     b.adopt_input_weight(self.stacked[row:row + p.shape[0]])
                     row += p.shape[0]
 
@@ -82,9 +87,8 @@ class PairMixer:
 
     def adopt_input_weight(self, rows: torch.Tensor) -> None:
         self.stacked = rows
-        ends = self.first_col[1:] + [rows.shape[0]]
-        for b, lo, hi in zip(self.branches, self.first_col, ends):
-            b.adopt_input_weight(rows[lo:hi])
+        for b, lo, n in zip(self.branches, self.first_col, self.part_rows):
+            b.adopt_input_weight(rows[lo:lo + n])
 
     def forward(self, x, ctx, proj=None):
         from ..engine.model import RunContext
