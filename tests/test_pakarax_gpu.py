@@ -143,7 +143,7 @@ def _slope_ref(q, ks, vs, seqs, scale, window, sink, slopes, dtype):
 
 
 SLOPE_CASES = [  # nq, nkv, d, [(start, n_new)], window
-    (8, 2, 96, [(0, 70), (130, 3), (0, 1)], None),
+    (8, 4, 112, [(0, 70), (130, 3), (0, 1)], None),
     (6, 1, 64, [(0, 129), (63, 2)], None),
     (4, 2, 80, [(0, 40), (100, 30)], 37),
     (3, 3, 40, [(0, 66)], None),
