@@ -78,7 +78,7 @@ constexpr int MAX_RANKS = 16;  // 8 is the portable cluster size; 16 where the d
 
 // TMA: the page tiles come by tensor-map loads (D a multiple of 64) and lie
 // swizzled, [D / 64][PAGE][64]; else by 16-byte copies into padded rows.
-template <int D, bool TMA>
+template <int D, bool TMA, bool PEN>
 __global__ void __launch_bounds__(DEC_THREADS + 32)
 attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
@@ -163,7 +163,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     // a distance bias: slope * (query position - key position) off every score; the
     // slopes are weights (no kernel writes them), times log2(e) like the scale
     float pen[2] = {0.0f, 0.0f};
-    if (slopes) {
+    if (PEN && slopes) {
 #pragma unroll
         for (int j = 0; j < 2; ++j)
             if (2 * (lane & 3) + j < nh) pen[j] = slopes[h0 + 2 * (lane & 3) + j] * LOG2E;
@@ -215,7 +215,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         // that the four warps are done with it; nothing else orders them page by page.
         if (warp < 4) {
             auto nothing = [&](int) { return false; };
-            attend_keys16<D, true>(qf, kbuf + (DEC_STAGES - 1) * TILE, vbuf + (DEC_STAGES - 1) * TILE, warp * 16,
+            attend_keys16<D, true, PEN>(qf, kbuf + (DEC_STAGES - 1) * TILE, vbuf + (DEC_STAGES - 1) * TILE, warp * 16,
                                    scale_log2, nothing, pen, 0, m, l, acc);
             reset();
             // the dry pass is this buffer's first use: done with it
@@ -280,7 +280,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                 if (tracing) waited += c2 - c0;
                 const int base = pg * PAGE;
                 auto visible = [&](int key) { return base + key >= lo && base + key <= pos; };
-                attend_keys16<D, true>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
+                attend_keys16<D, true, PEN>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
                                        pen, pos - base, m, l, acc);
                 __syncwarp();
                 if (lane == 0) sm100::mbar_arrive(&empty_bar[buf]);
@@ -310,7 +310,7 @@ attention_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
             const int base = pg * PAGE;
             const int lo_eff = dry ? 0x7fffffff : lo;
             auto visible = [&](int key) { return base + key >= lo_eff && base + key <= pos; };
-            attend_keys16<D, false>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
+            attend_keys16<D, false, PEN>(qf, kbuf + buf * TILE, vbuf + buf * TILE, warp * 16, scale_log2, visible,
                                     pen, pos - base, m, l, acc);
             if (tracing && !dry) attending += clock64() - c2;
             if (dry) {
@@ -529,7 +529,7 @@ const CUtensorMap* store_map(const void* base, long long rows, int D) {
     return &cache.emplace(key, m).first->second;
 }
 
-template <int D, bool TMA>
+template <int D, bool TMA, bool PEN>
 int launch_decode(const void* q, const void* k_pages, const void* v_pages, long long pool_pages,
                   const PagedKV& cache, const int* row_pos, const int* row_slot, void* out, float* partial,
                   int R, int nq, int n_splits, int window, float scale, const float* sink,
@@ -552,7 +552,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, long 
         mv = store_map(v_pages, rows, D);
         if (!mk || !mv) return RFX_ERR_UNSUPPORTED;
     }
-    auto kernel = attention_decode_kernel<D, TMA>;
+    auto kernel = attention_decode_kernel<D, TMA, PEN>;
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     dim3 grid(R, cache.n_kv_heads * n_htiles, n_splits);
@@ -615,9 +615,12 @@ int decode_entry(const void* q, const void* k_pages, const void* v_pages, const 
     const bool tma = tma_on && pool_pages > 0 && head_dim % 64 == 0 &&
                      ((reinterpret_cast<uintptr_t>(k_pages) | reinterpret_cast<uintptr_t>(v_pages)) & 15) == 0 &&
                      pool_pages * nkv * PAGE < 2147483647LL;
-#define RFX_GO(DD, T)                                                                                     \
-    launch_decode<DD, T>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, R, nq, \
-                         n_splits, window, scale, sink, slopes, cluster_merge, err, s)
+    // with slopes: the kernel's form that takes the distance term off the scores
+#define RFX_GO(DD, T)                                                                                              \
+    (slopes ? launch_decode<DD, T, true>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, \
+                                         R, nq, n_splits, window, scale, sink, slopes, cluster_merge, err, s)     \
+            : launch_decode<DD, T, false>(q, k_pages, v_pages, pool_pages, cache, row_pos, row_slot, out, partial, \
+                                          R, nq, n_splits, window, scale, sink, slopes, cluster_merge, err, s))
 #define RFX_CASE(DD)                                        \
     case DD:                                                \
         if (DD % 64 == 0 && tma) {                          \

@@ -119,10 +119,16 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
                 const int j = base + key;
                 return j <= row_pos[h] && j >= row_lo[h];
             };
-            // a distance bias: slope * (query position - key position) off the score
-            auto penalty = [&](int key, int h) { return row_pen[h] * (float)(row_pos[h] - (base + key)); };
-            attend_tile<D, 8>(qs + warp_row0 * LD, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, 0,
-                              scale_log2, visible, penalty, m, l, acc);
+            if (slopes) {
+                // a distance bias: slope * (query position - key position) off the score
+                auto penalty = [&](int key, int h) { return row_pen[h] * (float)(row_pos[h] - (base + key)); };
+                attend_tile<D, 8>(qs + warp_row0 * LD, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, 0,
+                                  scale_log2, visible, penalty, m, l, acc);
+            } else {  // the tile code as it is without the term (x - 0 folds away)
+                auto none = [](int, int) { return 0.0f; };
+                attend_tile<D, 8>(qs + warp_row0 * LD, kbuf + buf * PAGE * LD, vbuf + buf * PAGE * LD, 0,
+                                  scale_log2, visible, none, m, l, acc);
+            }
         }
         __syncthreads();
     }

@@ -218,9 +218,9 @@ __device__ __forceinline__ const __nv_bfloat16* tile_at(const __nv_bfloat16* til
 
 //   pen[2], dist0: a distance bias on the scores.  Tile key j lies dist0 - j
 //   positions before the query, and pen[i] * (dist0 - j) is taken off its scaled
-//   score for the thread's i-th head (slope times log2(e); 0.0f: no bias, the
-//   score's bits stay as they are)
-template <int D, bool SWZ = false, typename Visible>
+//   score for the thread's i-th head (slope times log2(e)).  PEN false: no such
+//   term, and the instructions are what they were without it
+template <int D, bool SWZ = false, bool PEN = false, typename Visible>
 __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], const __nv_bfloat16* ks,
                                               const __nv_bfloat16* vs, int key0, float scale_log2,
                                               Visible visible, const float (&pen)[2], int dist0,
@@ -237,11 +237,18 @@ __device__ __forceinline__ void attend_keys16(const uint32_t (&qf)[D / 16][2], c
     const int ka = key0 + (lane >> 2), kb = ka + 8;
     const bool va = visible(ka), vb = visible(kb);
     float v[4];
-    const float da = (float)(dist0 - ka), db = (float)(dist0 - kb);
-    v[0] = va ? s[0] * scale_log2 - pen[0] * da : -INFINITY;
-    v[1] = va ? s[1] * scale_log2 - pen[1] * da : -INFINITY;
-    v[2] = vb ? s[2] * scale_log2 - pen[0] * db : -INFINITY;
-    v[3] = vb ? s[3] * scale_log2 - pen[1] * db : -INFINITY;
+    if constexpr (PEN) {
+        const float da = (float)(dist0 - ka), db = (float)(dist0 - kb);
+        v[0] = va ? s[0] * scale_log2 - pen[0] * da : -INFINITY;
+        v[1] = va ? s[1] * scale_log2 - pen[1] * da : -INFINITY;
+        v[2] = vb ? s[2] * scale_log2 - pen[0] * db : -INFINITY;
+        v[3] = vb ? s[3] * scale_log2 - pen[1] * db : -INFINITY;
+    } else {
+        v[0] = va ? s[0] * scale_log2 : -INFINITY;
+        v[1] = va ? s[1] * scale_log2 : -INFINITY;
+        v[2] = vb ? s[2] * scale_log2 : -INFINITY;
+        v[3] = vb ? s[3] * scale_log2 : -INFINITY;
+    }
     float corr[2];
 #pragma unroll
     for (int j = 0; j < 2; ++j) {

@@ -96,18 +96,16 @@ struct Fuse {
     __nv_bfloat16* v_pages;
     rfx::PagedKV cache;
     int nq, nkv_in, head_dim;
-    // EPI 1: act_clamped != 0 makes the gated activation the clamped form,
-    // g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1),
-    // instead of silu(g) u
-    int act_clamped;
+    // EPI 4: EPI 1 with the clamped gated activation, g' = min(g, limit),
+    // u' = clamp(u, -limit, limit), g' sigmoid(alpha g') (u' + 1), instead of silu(g) u
     float act_alpha, act_limit;
 };
 
 // The gated activation of EPI 1 (results rounded to bfloat16 take the fast exponential
 // and division, as `silu_mul_for` does).
-template <typename TO>
+template <typename TO, bool CLAMPED>
 __device__ __forceinline__ float gated_act(float g, float u, const Fuse& f) {
-    if (f.act_clamped) {
+    if constexpr (CLAMPED) {
         g = fminf(g, f.act_limit);
         u = fminf(fmaxf(u, -f.act_limit), f.act_limit);
         if constexpr (sizeof(TO) == 2) return __fdividef(g, 1.0f + __expf(-f.act_alpha * g)) * (u + 1.0f);
@@ -129,6 +127,8 @@ __device__ __forceinline__ float gated_act(float g, float u, const Fuse& f) {
 // up_j) and y[r, j] = silu(gate_j) * up_j, so the SwiGLU activation costs no
 // launch and no round trip of the [R, 2I] intermediate
 // (src/kernels_cuda/silu_and_mul.cu:7-23 is the reference's separate kernel).
+// EPI 4: the same with the clamped gated activation (`gated_act`), a template
+// instance of its own, so that EPI 1's instructions are what they were.
 using rfx::silu_mul;
 using rfx::silu_mul_for;
 
@@ -321,7 +321,8 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int kb0 = z * per;
     const int nkb = max(0, min(num_kb, kb0 + per) - kb0);
     // rows of the tile that each rank of a K-split cluster finishes
-    const int mw = (EPI == 1) ? ((((bm + ksplit - 1) / ksplit) + 1) & ~1) : (bm + ksplit - 1) / ksplit;
+    constexpr bool GATED = EPI == 1 || EPI == 4;  // rows alternate gate, up; the epilogue writes their activation
+    const int mw = GATED ? ((((bm + ksplit - 1) / ksplit) + 1) & ~1) : (bm + ksplit - 1) / ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -561,7 +562,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
                         if (!dry) store4(y + (size_t)r * N + n, acc);
                     }
-                } else if (quads && EPI == 1) {
+                } else if (quads && GATED) {
                     for (int e = et; e < BN * mq; e += ET) {
                         const int rr = e / mq, ml4 = 4 * (e % mq), mm = z * mw + ml4;
                         const int r = r0 + rr, n = n0 + mm;
@@ -578,7 +579,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float f = rstd_s[rr];
                             acc.x *= f, acc.y *= f, acc.z *= f, acc.w *= f;
                         }
-                        const float o0 = gated_act<TO>(acc.x, acc.y, fuse), o1 = gated_act<TO>(acc.z, acc.w, fuse);
+                        const float o0 = gated_act<TO, EPI == 4>(acc.x, acc.y, fuse), o1 = gated_act<TO, EPI == 4>(acc.z, acc.w, fuse);
                         if (!dry) store2(y + (size_t)r * (N / 2) + n / 2, o0, o1);
                     }
                 } else if (quads && EPI == 2 && BN <= 64) {
@@ -644,7 +645,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         const int r = r0 + rr;
                         if (r < R && n0 + mm < N && !dry) rfx::st<TO>(y, (size_t)r * N + n0 + mm, acc);
                     }
-                } else if (EPI == 1) {
+                } else if (GATED) {
                     const int pw = mw / 2;
                     for (int e = et; e < BN * pw; e += ET) {
                         const int rr = e / pw, ml1 = 2 * (e % pw), mm = z * mw + ml1;
@@ -660,7 +661,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
                         const int r = r0 + rr;
                         if (r < R && n0 + mm + 1 < N && !dry)
-                            rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, gated_act<TO>(g, u, fuse));
+                            rfx::st<TO>(y, (size_t)r * (N / 2) + (n0 + mm) / 2, gated_act<TO, EPI == 4>(g, u, fuse));
                     }
                 } else {
                     for (int e = et; e < BN * mw; e += ET) {
@@ -705,7 +706,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                         for (int j = 0; j < 16; ++j) v[j] = 0.0f;
                     }
-                    if (EPI == 1) {
+                    if (GATED) {
                         // Rows alternate gate, up: lanes 2i and 2i + 1 hold one feature's
                         // pair.  Of every two columns the even lane finishes the first and
                         // the odd lane the second, after one exchange.
@@ -722,7 +723,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                             const float got = __shfl_xor_sync(0xffffffffu, even ? a1 : a0, 1);
                             const float gate = even ? a0 : got, up = even ? got : a1;
                             const int r = r0 + c * 16 + j + (even ? 0 : 1);
-                            const float o = gated_act<TO>(gate, up, fuse);
+                            const float o = gated_act<TO, EPI == 4>(gate, up, fuse);
                             if (pair_ok && r < R) rfx::st<TO>(y, (size_t)r * (N / 2) + n / 2, o);
                         }
                     } else {
@@ -890,7 +891,7 @@ int launch(const void* x, const void* W, void* y, int R, int N, int K, int kspli
     const int num_kb = (K + BK - 1) / BK;
     Cut cut = choose_cut(N, r_tiles, num_kb, ksplit_req, EPI == 3, BN);
     if (EPI == 3 && (r_tiles != 1 || BN % cut.ks)) return RFX_ERR_UNSUPPORTED;
-    if (EPI == 1 && (cut.bm & 1)) {  // pairs must not straddle tiles
+    if ((EPI == 1 || EPI == 4) && (cut.bm & 1)) {  // pairs must not straddle tiles
         cut.bm += 1;
         if (cut.bm > BM) return RFX_ERR_UNSUPPORTED;
         cut.tiles = (N + cut.bm - 1) / cut.bm;
@@ -999,13 +1000,12 @@ extern "C" int rfx_gemm_bf16_tc_glu_clamped(const void* x, const void* W, void* 
     if (int c = check_common(x, W, R, N, K)) return c;
     if (N & 1) return RFX_ERR_BAD_ARG;
     cudaStream_t s = (cudaStream_t)stream;
+    if (R > 64) return RFX_ERR_UNSUPPORTED;  // a decode-sized batch's form
     Fuse f{};
-    f.act_clamped = 1;
     f.act_alpha = alpha;
     f.act_limit = limit;
-    if (y_dt == RFX_DT_F32) return dispatch<float, 1, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
-    if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 1, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
-    return RFX_ERR_BAD_ARG;
+    if (y_dt == RFX_DT_BF16) return dispatch<__nv_bfloat16, 4, false>(x, W, y, R, N, K, ksplit, f, nullptr, err, s);
+    return RFX_ERR_UNSUPPORTED;
 }
 
 // The product as a delta of the residual stream, for R <= 64:
